@@ -1,0 +1,454 @@
+#!/usr/bin/env python
+"""Benchmark of the resampling path: output Gvoxel/s of one forward pass of the batched
+CropRandomWithAffine patch extraction (per GPU: 8 CT-like volumes (1,256,512,512) fp16,
+64 rotated 96^3 patches per volume -> (512,1,96,96,96)), sharded over N GPUs by volume with
+no communication, plus the roofline fraction of its kernel, CPU baselines and, at N = 1, the
+Resize and RandomAffine configurations as extra lines of the same JSON object.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one pass of the path over the whole workload (one kernel launch per GPU).
+Inputs are synthetic (seeded), already resident in HBM for `value`; `e2e` times the public
+call with pinned HOST inputs and a host copy of the result inside the timed region.
+Inputs (1.07 GB per GPU) are far larger than L2, so no explicit L2 flush is needed.
+
+`--impl reference` runs the reference's own CUDA kernels (oracle/_ref, compiled unmodified for
+sm_100a) on the same workload; if that build is absent it times the CPU restatement instead.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PATCH = 96
+
+
+# ----------------------------------------------------------------------------- synthetic data
+def ct_like(shape, seed, device):
+    """int16 CT-like values ~N(-300,400) clipped to [-1024,3071], scaled to [0,1], fp16."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    v = torch.empty(shape, device=device, dtype=torch.float32).normal_(-300, 400, generator=g)
+    v = v.round_().clamp_(-1024, 3071)
+    return ((v + 1024) / 4095).half()
+
+
+def crop_rois(n_vol, per_vol, vol_shape, seed):
+    """rois of CropRandomWithAffine (medvision/aug_cuda_batch/aug_spatial.py:674-715): random
+    patch position, rotation about z within +-20 degrees, scale 0.9-1.1, no shift."""
+    g = torch.Generator().manual_seed(seed)
+    R = n_vol * per_vol
+    D, H, W = vol_shape
+    b = torch.arange(n_vol).repeat_interleave(per_vol).float().view(-1, 1)
+    scale = torch.rand(R, 1, generator=g) * 0.2 + 0.9
+    ext = torch.tensor([W, H, D], dtype=torch.float32)
+    start = torch.rand(R, 3, generator=g) * (ext - PATCH)
+    centre = start + PATCH / 2
+    ang = torch.zeros(R, 3)
+    ang[:, 2] = (torch.rand(R, generator=g) * 2 - 1) * math.radians(20)
+    return torch.cat([b, centre, (PATCH / scale).expand(R, 3), ang], 1)
+
+
+def workload_c5(device, rank, small=False):
+    n_vol, per_vol = (2, 16) if small else (8, 64)
+    shape = (1, 256, 512, 512)
+    vol = ct_like((n_vol,) + shape, 5 + rank, device)
+    rois = crop_rois(n_vol, per_vol, shape[1:], 5 + rank)
+    return dict(name="CropRandomWithAffine %dx(1,256,512,512) fp16 -> (%d,1,96,96,96), z-rotation +-20deg, "
+                     "scale 0.9-1.1" % (n_vol, n_vol * per_vol),
+                features=vol, rois=rois, out_size=(PATCH,) * 3, order=1)
+
+
+def workload_c3(device, rank, small=False):
+    n = 1 if small else 4
+    vol = ct_like((n, 1, 160, 512, 512), 3 + rank, device)
+    rois = torch.tensor([[i, 256, 256, 80, 512, 512, 160, 0, 0, 0] for i in range(n)], dtype=torch.float32)
+    return dict(name="Resize %dx(1,160,512,512) fp16 -> (128,256,256)" % n, features=vol, rois=rois,
+                out_size=(128, 256, 256), order=1)
+
+
+def workload_c4(device, rank, small=False):
+    n = 4 if small else 16
+    g = torch.Generator(device=device).manual_seed(4 + rank)
+    x = torch.empty((n, 1, 128, 128, 128), device=device).normal_(generator=g)
+    k = torch.arange(-12, 13, device=device).float()
+    k = torch.exp(-k * k / 32)
+    k /= k.sum()
+    for d in (2, 3, 4):  # separable Gaussian blur, sigma 4
+        shp = [1, 1, 1, 1, 1]
+        shp[d] = 25
+        pad = [0, 0, 0]
+        pad[d - 2] = 12
+        x = torch.nn.functional.conv3d(x, k.view(shp), padding=pad)
+    x = (x / x.std()).half()
+    gc = torch.Generator().manual_seed(4 + rank)
+    ang = (torch.rand(n, 3, generator=gc) * 2 - 1) * math.radians(30)
+    sc = torch.rand(n, 1, generator=gc) * 0.4 + 0.8
+    sh = (torch.rand(n, 3, generator=gc) * 2 - 1) * 10
+    rois = torch.cat([torch.arange(n).float().view(-1, 1), 64 - sh / sc, (128 / sc).expand(n, 3), ang], 1)
+    return dict(name="RandomAffine (%d,1,128,128,128) fp16, rotation +-30deg x3, scale 0.8-1.2, shift +-10" % n,
+                features=x, rois=rois, out_size=(128, 128, 128), order=1)
+
+
+WORKLOADS = {"c5": workload_c5, "c3": workload_c3, "c4": workload_c4}
+
+
+# ----------------------------------------------------------------------------- implementations
+class Ours:
+    name = "ours"
+
+    def __init__(self):
+        from medvision_b200 import _C
+        from medvision_b200.ops import affine_3d
+        self._C = _C
+        self.affine_3d = affine_3d
+
+    def forward_into(self, feat, rois, out, order):
+        self._C.affine_3d(feat, rois, out, *out.shape[2:], 1.0, 1, True, order)
+
+    def backward_into(self, grad, rois, gin, order):
+        self._C.roi_align_rotated_3d_backward(grad, rois, gin, *grad.shape[2:], 1.0, 1, True, order)
+
+    def public_forward(self, feat, rois, out_size, order):
+        return self.affine_3d(feat, rois, tuple(out_size), 1.0, 1, True, order)
+
+
+class ReferenceCuda:
+    """The reference's own kernels (oracle/_ref), called like medvision/ops/cuda_fun_tools.py:48-91."""
+    name = "reference"
+
+    def __init__(self):
+        from oracle import ref
+        self.m = ref.module()
+
+    def forward_into(self, feat, rois, out, order):
+        self.m.affine_3d(feat, rois, out, *out.shape[2:], 1.0, 1, True, order)
+
+    def backward_into(self, grad, rois, gin, order):
+        self.m.roi_align_rotated_3d_backward(grad, rois, gin, *grad.shape[2:], 1.0, 1, True, order)
+
+    def public_forward(self, feat, rois, out_size, order):
+        out = feat.new_zeros((rois.size(0), feat.size(1)) + tuple(out_size))
+        self.m.affine_3d(feat, rois.type(feat.type()), out, *out_size, 1.0, 1, True, order)
+        return out
+
+
+# ----------------------------------------------------------------------------- measurement
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x, world):
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return x
+
+
+def time_steps(fn, steps, warmup, world):
+    """W untimed steps, then exactly K steps between barrier + synchronize, timed with CUDA
+    events on the launching (current) stream; returns ms for the K steps, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    barrier(world)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world)
+
+
+def touched_elements(feat, rois, out_size, order):
+    """Exact count of distinct input elements read by the forward (mark pass, untimed)."""
+    from medvision_b200 import _lib
+    mask = torch.zeros(feat.shape, dtype=torch.uint8, device=feat.device)
+    N, C, D, H, W = feat.shape
+    rc = _lib.lib.mvr_roi_resample_touched(rois.data_ptr(), mask.data_ptr(), _lib.MVR_F16 if feat.dtype == torch.float16
+                                           else _lib.MVR_F32, 3, _lib.MVR_ROI_ROTATED, N, C, D, H, W, rois.size(0),
+                                           rois.size(1), *out_size, 1.0, 1, 1, order,
+                                           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.strerror(rc)
+    total = 0
+    for i in range(N):  # per volume: keeps the reduction's temporaries small
+        total += int(mask[i].sum(dtype=torch.int64).item())
+    return total
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def cpu_baseline_port(wl, budget_s=12.0):
+    """The CPU restatement of the reference kernels on the host cores, on a bounded sample of
+    the same workload: the first rois of the first volume."""
+    from oracle import port
+    feat = wl["features"][:1].cpu()
+    rois = wl["rois"][wl["rois"][:, 0] == 0].to(feat.dtype).cpu()
+    threads = port.max_threads()
+    n = min(2, rois.size(0))
+    t0 = time.perf_counter()
+    port.forward(feat, rois[:n], wl["out_size"], port.KIND_ROTATED, 1.0, 1, True, wl["order"])
+    dt = time.perf_counter() - t0
+    per_roi = dt / n
+    n2 = int(max(n, min(rois.size(0), budget_s / max(per_roi, 1e-6))))
+    t0 = time.perf_counter()
+    out = port.forward(feat, rois[:n2], wl["out_size"], port.KIND_ROTATED, 1.0, 1, True, wl["order"])
+    dt = time.perf_counter() - t0
+    return {"value": out.numel() / dt / 1e9, "unit": "Gvoxel/s", "cores": threads, "kind": "port",
+            "sample": "%d of %d rois of volume 0, %.1f s" % (n2, wl["rois"].size(0), dt)}
+
+
+def cpu_baseline_scipy():
+    """What the reference's numpy augmentations call for the same job
+    (medvision/aug_cpu/aug_spatial.py:475 rotate, :99 zoom), single-threaded scipy."""
+    try:
+        import numpy as np
+        import scipy.ndimage as ndi
+    except ImportError:
+        return None
+    rng = np.random.default_rng(0)
+    v = rng.random((1, PATCH, PATCH, PATCH), dtype=np.float32)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 2.0:
+        ndi.rotate(v, 15.0, axes=(3, 2), reshape=False, order=1, mode="constant", cval=0)
+        reps += 1
+    rot = reps * v.size / (time.perf_counter() - t0) / 1e9
+    t0 = time.perf_counter()
+    ndi.zoom(v, (1, 1.1, 1.1, 1.1), order=2)
+    zoom = v.size * 1.1 ** 3 / (time.perf_counter() - t0) / 1e9
+    return {"unit": "Gvoxel/s", "cores": 1, "kind": "scipy.ndimage calls of the reference's aug_cpu",
+            "rotate_order1": rot, "zoom_order2": zoom, "sample": "(1,96,96,96) float32 patch"}
+
+
+def measure(impl, wl, steps, warmup, world, backward=False):
+    feat, rois = wl["features"], wl["rois"].to(wl["features"].dtype).cuda()
+    out = torch.empty((rois.size(0), feat.size(1)) + tuple(wl["out_size"]), dtype=feat.dtype, device="cuda")
+    if not backward:
+        ms = time_steps(lambda: impl.forward_into(feat, rois, out, wl["order"]), steps, warmup, world)
+        return ms / steps, out
+    g = torch.Generator(device="cuda").manual_seed(1)
+    grad = torch.empty_like(out).normal_(generator=g)
+    gin = torch.empty_like(feat)
+
+    def step():
+        impl.forward_into(feat, rois, out, wl["order"])
+        gin.zero_()  # part of every backward: the op accumulates into a zeroed gradient
+        impl.backward_into(grad, rois, gin, wl["order"])
+    ms = time_steps(step, steps, warmup, world)
+    return ms / steps, out
+
+
+def measure_e2e(impl, wl, steps, warmup, world):
+    """Public call with HOST buffers: pinned inputs -> device, resample, result -> pinned host."""
+    feat_h = wl["features"].cpu().pin_memory()
+    rois_h = wl["rois"].pin_memory()
+    out_shape = (rois_h.size(0), feat_h.size(1)) + tuple(wl["out_size"])
+    out_h = torch.empty(out_shape, dtype=feat_h.dtype).pin_memory()
+
+    def step():
+        f = feat_h.cuda(non_blocking=True)
+        r = rois_h.cuda(non_blocking=True)
+        o = impl.public_forward(f, r, wl["out_size"], wl["order"])
+        out_h.copy_(o, non_blocking=True)
+    ms = time_steps(step, steps, warmup, world) / steps
+    h2d = feat_h.numel() * feat_h.element_size() + rois_h.numel() * rois_h.element_size()
+    d2h = out_h.numel() * out_h.element_size()
+    return ms, h2d, d2h, out_h
+
+
+def run_cpu_reference(args, rank):
+    """Fallback of --impl reference when the reference's CUDA build is absent: the CPU
+    restatement with all host threads on a bounded sample per step."""
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload]("cpu", 0, small=True)
+    base = cpu_baseline_port(wl, budget_s=8.0)
+    line = {"impl": "reference", "metric": "resampled Gvoxel/s (fwd)", "value": base["value"], "unit": "Gvoxel/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": wl["name"], "device": "cpu"}, "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "Gvoxel/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5")
+    ap.add_argument("--small", action="store_true", help="reduced copy of the workload (for profiler captures)")
+    ap.add_argument("--kernel-only", action="store_true", help="skip e2e, CPU baselines and the extra configurations")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        from oracle import ref
+        if not (ref.available() and torch.cuda.is_available()):
+            run_cpu_reference(args, int(os.environ.get("RANK", "0")))
+            return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: medvision_b200 has no CPU path")
+
+    rank, world, local = dist_setup(args.gpus)
+    impl = Ours() if args.impl == "ours" else ReferenceCuda()
+    wl = WORKLOADS[args.workload]("cuda", rank, small=args.small)
+    n_out = wl["rois"].size(0) * wl["features"].size(1) * math.prod(wl["out_size"])
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms, out = measure(impl, wl, args.steps, args.warmup, world)
+    clocks = sampler.stop() if rank == 0 else None
+    value = world * n_out / (ms * 1e-3) / 1e9
+
+    line = {"metric": "resampled Gvoxel/s (fwd)", "value": value, "unit": "Gvoxel/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": wl["name"], "sharding": "by volume, %d GPU(s), no collective" % world,
+                       "l2": "inputs (%.2f GB per GPU) larger than L2, no flush" %
+                             (wl["features"].numel() * 2 / 1e9),
+                       "sampling_ratio": 1, "order": 1, "aligned": True},
+            "gpu_launches": args.steps, "clocks": clocks}
+    if args.impl == "reference":
+        line["impl"] = "reference"
+        line["config"]["device"] = "cuda: the reference's own kernels, compiled unmodified for sm_100a"
+
+    # roofline of the dominant (only) kernel: algorithmic bytes / measured launch duration
+    e = wl["features"].element_size()
+    rois_dev = wl["rois"].to(wl["features"].dtype).cuda()
+    U = touched_elements(wl["features"], rois_dev, wl["out_size"], wl["order"])
+    alg_bytes = e * (U + n_out) + rois_dev.numel() * e
+    peak, peak_src = load_peaks()
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
+                        "distinct_input_elements": U, "output_elements": n_out,
+                        "frac_of_8000_nominal": achieved / 8000.0}
+
+    if not args.kernel_only:
+        ems, h2d, d2h, _ = measure_e2e(impl, wl, max(2, args.steps // 4), 3, world)
+        line["e2e"] = {"value": world * n_out / (ems * 1e-3) / 1e9, "unit": "Gvoxel/s", "ms_per_step": ems,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if args.impl == "reference" and rank == 0:
+            line["cpu_baseline"] = {"value": value, "unit": "Gvoxel/s", "cores": 0, "kind": "reference",
+                                    "sample": "whole workload on the GPU (the reference path has no CPU implementation)"}
+        if world == 1 and args.impl == "ours":
+            line["cpu_baseline"] = cpu_baseline_port(wl)
+            sp = cpu_baseline_scipy()
+            if sp:
+                line["cpu_baseline_aug_cpu"] = sp
+        if world == 1 and args.workload == "c5" and not args.small:
+            extra = []
+            del out
+            wl = None
+            torch.cuda.empty_cache()
+            for key, bwd in (("c3", False), ("c4", False), ("c4", True)):
+                w2 = WORKLOADS[key]("cuda", 0)
+                n2 = w2["rois"].size(0) * math.prod(w2["out_size"])
+                m2, _ = measure(impl, w2, max(args.steps, 20), args.warmup, 1, backward=bwd)
+                r2 = w2["rois"].to(w2["features"].dtype).cuda()
+                U2 = touched_elements(w2["features"], r2, w2["out_size"], 1)
+                b2 = 2 * (U2 + n2) + r2.numel() * 2
+                if bwd:
+                    b2 += 2 * (n2 + w2["features"].numel()) + r2.numel() * 2
+                extra.append({"workload": w2["name"], "pass": "fwd+bwd" if bwd else "fwd", "ms_per_step": m2,
+                              "gvoxel_per_s": n2 / (m2 * 1e-3) / 1e9, "algorithmic_bytes": b2,
+                              "achieved_gbs": b2 / (m2 * 1e-3) / 1e9, "frac_of_peak": b2 / (m2 * 1e-3) / 1e9 / peak,
+                              "note": "input fits in L2" if key == "c4" else "input larger than L2"})
+            line["other_configs"] = extra
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

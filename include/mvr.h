@@ -1,0 +1,161 @@
+/* medvision-b200 resampling library: C ABI.
+ *
+ * B200 (sm_100a) implementation of the RoI Align / RoI Align Rotated / affine_{2d,3d}
+ * gather-interpolate path of MedVision.  The ten `mvr_<name>` entry points at the end are
+ * what the reference's Python layer binds as `medvision._C.<name>`
+ * (medvision/csrc/vision.cpp:34-48,74-75); each one takes the same arguments in the same
+ * order, with every tensor replaced by a device pointer plus its sizes, and a stream.
+ *
+ * Conventions
+ *  - All data pointers are DEVICE pointers on the current device; tensors are contiguous
+ *    NC[D]HW, rois are (R, roi_width) in the SAME element type as the features
+ *    (medvision/ops/cuda_fun_tools.py:37,82 casts them before the call).
+ *      box 2D      (R,5)  [batch, x1, y1, x2, y2]              medvision/ops/roi_align_nd.py:162-165
+ *      box 3D      (R,7)  [batch, x1, y1, z1, x2, y2, z2]
+ *      rotated 2D  (R,6)  [batch, cx, cy, w, h, angle]         medvision/ops/roi_align_rotated_nd.py:171-175
+ *      rotated 3D  (R,10) [batch, cx, cy, cz, w, h, d, angle_x, angle_y, angle_z]   (radians)
+ *  - Calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ *    default stream), never synchronise and never allocate.
+ *  - Return value: MVR_OK or a negative MVR_ERR_* code; nothing is launched on error.
+ *    `mvr_strerror` gives the message, worded as the reference's AT_ERROR text where one
+ *    exists ("wrong roi size! size_rois should be 10", medvision/csrc/roi_align_rotated_3d.h:34-36).
+ *  - `status` is an optional device int (may be NULL).  A roi whose batch index is outside
+ *    [0, N) is not sampled (the reference would read out of bounds): its outputs are zero,
+ *    its gradient is dropped, and bit MVR_STATUS_BAD_BATCH_INDEX is OR-ed into *status.
+ *  - There is no CPU implementation: a missing GPU or library is an error, as in the
+ *    reference ("RoIAlignRotated is not implemented on CPU", roi_align_rotated_3d.h:93-95).
+ */
+#ifndef MVR_H_
+#define MVR_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types (the reference dispatches float, double and half:
+ * AT_DISPATCH_FLOATING_TYPES_AND_HALF, medvision/csrc/cuda/roi_align_rotated_3d_cuda.cu:14) */
+#define MVR_F32 0
+#define MVR_F16 1
+#define MVR_F64 2
+
+#define MVR_ROI_BOX 0
+#define MVR_ROI_ROTATED 1
+
+#define MVR_OK 0
+#define MVR_ERR_DTYPE (-1)
+#define MVR_ERR_NDIM (-2)
+#define MVR_ERR_ROI_KIND (-3)
+#define MVR_ERR_ORDER (-4)
+#define MVR_ERR_SHAPE (-5)
+#define MVR_ERR_NULL (-6)
+#define MVR_ERR_ROI_WIDTH (-7)
+#define MVR_ERR_LAUNCH (-8)
+#define MVR_ERR_TOO_LARGE (-9)
+#define MVR_ERR_NO_DEVICE (-10)
+
+#define MVR_STATUS_BAD_BATCH_INDEX 1
+
+const char* mvr_strerror(int code);
+int mvr_version(void);
+
+/* Which float products are fused into the following addition (bit set of the contraction
+ * pattern; half arithmetic never fuses).  The default reproduces the reference build
+ * (nvcc -fmad=true).  Returns the previous value.  Process-wide; not a per-call option. */
+int mvr_set_float_contraction(int bits);
+int mvr_get_float_contraction(void);
+
+/* General forward: output[r, c, p] = mean over the roi bin's sub-samples of
+ * interp(features[batch(r), c], sample position).
+ * Replaces the six forward launchers (medvision/csrc/cuda/roi_align_{2d,3d}_cuda.cu:5-30,
+ * roi_align_rotated_{2d,3d}_cuda.cu:5-30, medvision/csrc/cuda_aug/affine_{2d,3d}_cuda.cu:5-30).
+ * ndim 2: D and od must be 1.  roi_width is rois.size(1) and is checked against (ndim, roi_kind).
+ * order 0 = nearest, 1 = linear.  R == 0 is a no-op. */
+int mvr_roi_resample_fwd(const void* features, const void* rois, void* output, int dtype, int ndim, int roi_kind,
+                         int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                         int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                         int* status, void* stream);
+
+/* General backward: grad_in += scatter of grad_out * tap weight / sample count.  grad_in has
+ * the feature shape, must be zero-filled by the caller (as the reference's Python does,
+ * medvision/ops/roi_align_rotated_nd.py:148) and is accumulated into with atomics in the
+ * element type, like the reference (medvision/csrc/cuda/roi_align_rotated_3d_cuda_kernel.cuh:251-260).
+ * Replaces the four backward launchers (medvision/csrc/cuda/roi_align*_cuda.cu:32-55). */
+int mvr_roi_resample_bwd(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim, int roi_kind,
+                         int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                         int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                         int* status, void* stream);
+
+/* Measurement utility; has no counterpart in the reference.  Sets mask[b, c, voxel] = 1 (bytes,
+ * feature shape, zero-filled by the caller) for every input element that a tap of the
+ * corresponding forward call reads.  The count of set bytes is the "distinct input elements
+ * touched" term of the forward's algorithmic byte count. */
+int mvr_roi_resample_touched(const void* rois, unsigned char* mask, int dtype, int ndim, int roi_kind,
+                             int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                             int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                             void* stream);
+
+/* ---- the reference's extension surface, one entry per `m.def` ------------------------- */
+
+/* medvision/csrc/vision.cpp:34  roi_align_2d_forward(input, rois, output, oh, ow, spatial_scale, sampling_ratio, order)
+ * (medvision/csrc/roi_align_2d.h) */
+int mvr_roi_align_2d_forward(const void* input, const void* rois, void* output, int dtype,
+                             int64_t N, int64_t C, int64_t H, int64_t W, int64_t R, int roi_width,
+                             int oh, int ow, float spatial_scale, int sampling_ratio, int order,
+                             int* status, void* stream);
+/* medvision/csrc/vision.cpp:35  roi_align_2d_backward(top_grad, rois, bottom_grad, oh, ow, spatial_scale, sampling_ratio, order) */
+int mvr_roi_align_2d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype,
+                              int64_t N, int64_t C, int64_t H, int64_t W, int64_t R, int roi_width,
+                              int oh, int ow, float spatial_scale, int sampling_ratio, int order,
+                              int* status, void* stream);
+/* medvision/csrc/vision.cpp:37  roi_align_3d_forward(input, rois, output, od, oh, ow, spatial_scale, sampling_ratio, order)
+ * (medvision/csrc/roi_align_3d.h) */
+int mvr_roi_align_3d_forward(const void* input, const void* rois, void* output, int dtype,
+                             int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                             int od, int oh, int ow, float spatial_scale, int sampling_ratio, int order,
+                             int* status, void* stream);
+/* medvision/csrc/vision.cpp:38  roi_align_3d_backward */
+int mvr_roi_align_3d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype,
+                              int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                              int od, int oh, int ow, float spatial_scale, int sampling_ratio, int order,
+                              int* status, void* stream);
+/* medvision/csrc/vision.cpp:40-41  roi_align_rotated_2d_forward(input, rois, output, oh, ow, spatial_scale,
+ * sampling_ratio, aligned, order)  (medvision/csrc/roi_align_rotated_2d.h) */
+int mvr_roi_align_rotated_2d_forward(const void* input, const void* rois, void* output, int dtype,
+                                     int64_t N, int64_t C, int64_t H, int64_t W, int64_t R, int roi_width,
+                                     int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                                     int* status, void* stream);
+/* medvision/csrc/vision.cpp:42-43  roi_align_rotated_2d_backward */
+int mvr_roi_align_rotated_2d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype,
+                                      int64_t N, int64_t C, int64_t H, int64_t W, int64_t R, int roi_width,
+                                      int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                                      int* status, void* stream);
+/* medvision/csrc/vision.cpp:45-46  roi_align_rotated_3d_forward(input, rois, output, od, oh, ow, spatial_scale,
+ * sampling_ratio, aligned, order)  (medvision/csrc/roi_align_rotated_3d.h:71-96) */
+int mvr_roi_align_rotated_3d_forward(const void* input, const void* rois, void* output, int dtype,
+                                     int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                                     int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned,
+                                     int order, int* status, void* stream);
+/* medvision/csrc/vision.cpp:47-48  roi_align_rotated_3d_backward  (medvision/csrc/roi_align_rotated_3d.h:98-117) */
+int mvr_roi_align_rotated_3d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype,
+                                      int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                                      int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned,
+                                      int order, int* status, void* stream);
+/* medvision/csrc/vision.cpp:74  affine_2d(input, rois, output, oh, ow, spatial_scale, sampling_ratio, aligned, order)
+ * (medvision/csrc/affine_2d.h) -- forward only */
+int mvr_affine_2d(const void* input, const void* rois, void* output, int dtype,
+                  int64_t N, int64_t C, int64_t H, int64_t W, int64_t R, int roi_width,
+                  int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                  int* status, void* stream);
+/* medvision/csrc/vision.cpp:75  affine_3d(input, rois, output, od, oh, ow, spatial_scale, sampling_ratio, aligned, order)
+ * (medvision/csrc/affine_3d.h:40-65) -- forward only */
+int mvr_affine_3d(const void* input, const void* rois, void* output, int dtype,
+                  int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                  int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                  int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MVR_H_ */

@@ -1,0 +1,221 @@
+// C ABI of the resampling library (declared in include/mvr.h): argument checks, kernel
+// selection and launch.  No torch types; device pointers and sizes only.
+#include <cuda_runtime.h>
+#include <atomic>
+
+#include "../../include/mvr.h"
+#include "mvr_generic.cuh"
+#include "mvr_stream3d.cuh"
+
+namespace {
+
+using namespace mvr;
+
+// Float contraction pattern of the reference build (see mvr_arith.cuh).
+// Found by matching the reference's own kernels bit for bit on a B200 (float32, all roi
+// kinds): every family fuses its first product, the 3D rotation adds the hoisted R_i3*z
+// with a plain add, and R22 = sa*sb*sg + ca*cg fuses its SECOND product.
+std::atomic<int> g_contraction(kReferenceContraction);
+
+int roi_width_of(int ndim, int kind) { return kind == KIND_BOX ? (ndim == 2 ? 5 : 7) : (ndim == 2 ? 6 : 10); }
+
+int check_common(const void* a, const void* rois, void* b, int dtype, int ndim, int kind, int64_t N, int64_t C,
+                 int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh, int ow, int order) {
+  if (dtype != MVR_F32 && dtype != MVR_F16 && dtype != MVR_F64) return MVR_ERR_DTYPE;
+  if (ndim != 2 && ndim != 3) return MVR_ERR_NDIM;
+  if (kind != MVR_ROI_BOX && kind != MVR_ROI_ROTATED) return MVR_ERR_ROI_KIND;
+  if (order != 0 && order != 1) return MVR_ERR_ORDER;
+  if (roi_width != roi_width_of(ndim, kind)) return MVR_ERR_ROI_WIDTH;
+  if (N < 0 || C < 0 || R < 0 || D < 1 || H < 1 || W < 1 || od < 1 || oh < 1 || ow < 1) return MVR_ERR_SHAPE;
+  if (ndim == 2 && (D != 1 || od != 1)) return MVR_ERR_SHAPE;
+  if (D > INT32_MAX || H > INT32_MAX || W > INT32_MAX || N > INT32_MAX || C > INT32_MAX || R > INT32_MAX)
+    return MVR_ERR_TOO_LARGE;
+  if (R > 0 && C > 0 && (!a || !rois || !b)) return MVR_ERR_NULL;
+  return MVR_OK;
+}
+
+Params make_params(const void* in, const void* rois, void* out, int ndim, int kind, int64_t N, int64_t C, int64_t D,
+                   int64_t H, int64_t W, int64_t R, int od, int oh, int ow, float spatial_scale, int sampling_ratio,
+                   int aligned, int order, int* status) {
+  Params p;
+  p.in = in; p.rois = rois; p.out = out; p.status = status;
+  p.ndim = ndim; p.kind = kind; p.order = order; p.aligned = aligned ? 1 : 0; p.sampling_ratio = sampling_ratio;
+  p.fm = g_contraction.load();
+  p.N = (int)N; p.C = (int)C; p.D = (int)D; p.H = (int)H; p.W = (int)W; p.R = (int)R;
+  p.od = od; p.oh = oh; p.ow = ow;
+  p.spatial_scale = spatial_scale;
+  p.vol = (long long)D * H * W;
+  p.ovol = (long long)od * oh * ow;
+  p.tiles_per_vol = (int)((p.ovol + kGenericThreads - 1) / kGenericThreads);
+  return p;
+}
+
+template <typename T>
+int launch_generic(const Params& p, bool fwd, cudaStream_t st) {
+  const long long ctas = (long long)p.R * p.C * p.tiles_per_vol;
+  if (ctas > 0x7fffffffLL) return MVR_ERR_TOO_LARGE;
+  const dim3 grid((unsigned)ctas), block(kGenericThreads);
+  if (fwd) {
+    if (p.ndim == 2) resample_fwd_generic<T, 2><<<grid, block, 0, st>>>(p);
+    else resample_fwd_generic<T, 3><<<grid, block, 0, st>>>(p);
+  } else {
+    if (p.ndim == 2) resample_bwd_generic<T, 2><<<grid, block, 0, st>>>(p);
+    else resample_bwd_generic<T, 3><<<grid, block, 0, st>>>(p);
+  }
+  return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
+}
+
+template <typename T>
+int launch_mark(const Params& p, cudaStream_t st) {
+  const long long ctas = (long long)p.R * p.C * p.tiles_per_vol;
+  if (ctas > 0x7fffffffLL) return MVR_ERR_TOO_LARGE;
+  if (p.ndim == 2) resample_mark_generic<T, 2><<<(unsigned)ctas, kGenericThreads, 0, st>>>(p);
+  else resample_mark_generic<T, 3><<<(unsigned)ctas, kGenericThreads, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
+}
+
+int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
+  if (p.R == 0 || p.C == 0) return MVR_OK;
+  if (fwd) {
+    int rc = try_launch_stream3d(p, dtype, st);
+    if (rc != MVR_STREAM3D_NOT_APPLICABLE) return rc;
+  }
+  switch (dtype) {
+    case MVR_F32: return launch_generic<float>(p, fwd, st);
+    case MVR_F16: return launch_generic<__half>(p, fwd, st);
+    default: return launch_generic<double>(p, fwd, st);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* mvr_strerror(int code) {
+  switch (code) {
+    case MVR_OK: return "ok";
+    case MVR_ERR_DTYPE: return "unsupported element type (float32, float16, float64 only)";
+    case MVR_ERR_NDIM: return "ndim must be 2 or 3";
+    case MVR_ERR_ROI_KIND: return "roi kind must be box or rotated";
+    case MVR_ERR_ORDER: return "only support order = 0 (nearest) or 1 (linear)";
+    case MVR_ERR_SHAPE: return "bad tensor shape";
+    case MVR_ERR_NULL: return "null data pointer";
+    case MVR_ERR_ROI_WIDTH: return "wrong roi size!";
+    case MVR_ERR_LAUNCH: return "CUDA kernel launch failed";
+    case MVR_ERR_TOO_LARGE: return "problem too large for one launch";
+    case MVR_ERR_NO_DEVICE: return "no CUDA device";
+    default: return "unknown error";
+  }
+}
+
+int mvr_version(void) { return 1; }
+
+int mvr_set_float_contraction(int bits) { return g_contraction.exchange(bits & 0x00ffffff); }
+int mvr_get_float_contraction(void) { return g_contraction.load(); }
+
+int mvr_roi_resample_fwd(const void* features, const void* rois, void* output, int dtype, int ndim, int roi_kind,
+                         int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                         int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                         int* status, void* stream) {
+  int rc = check_common(features, rois, output, dtype, ndim, roi_kind, N, C, D, H, W, R, roi_width, od, oh, ow, order);
+  if (rc != MVR_OK) return rc;
+  Params p = make_params(features, rois, output, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow, spatial_scale,
+                         sampling_ratio, aligned, order, status);
+  return dispatch(p, dtype, true, (cudaStream_t)stream);
+}
+
+int mvr_roi_resample_bwd(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim, int roi_kind,
+                         int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                         int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                         int* status, void* stream) {
+  int rc = check_common(grad_out, rois, grad_in, dtype, ndim, roi_kind, N, C, D, H, W, R, roi_width, od, oh, ow, order);
+  if (rc != MVR_OK) return rc;
+  Params p = make_params(grad_out, rois, grad_in, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow, spatial_scale,
+                         sampling_ratio, aligned, order, status);
+  return dispatch(p, dtype, false, (cudaStream_t)stream);
+}
+
+int mvr_roi_resample_touched(const void* rois, unsigned char* mask, int dtype, int ndim, int roi_kind, int64_t N,
+                             int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh,
+                             int ow, float spatial_scale, int sampling_ratio, int aligned, int order, void* stream) {
+  int rc = check_common(rois, rois, mask, dtype, ndim, roi_kind, N, C, D, H, W, R, roi_width, od, oh, ow, order);
+  if (rc != MVR_OK) return rc;
+  Params p = make_params(nullptr, rois, mask, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow, spatial_scale,
+                         sampling_ratio, aligned, order, nullptr);
+  if (p.R == 0 || p.C == 0) return MVR_OK;
+  switch (dtype) {
+    case MVR_F32: return launch_mark<float>(p, (cudaStream_t)stream);
+    case MVR_F16: return launch_mark<__half>(p, (cudaStream_t)stream);
+    default: return launch_mark<double>(p, (cudaStream_t)stream);
+  }
+}
+
+// ---- the reference's extension surface --------------------------------------------------
+// Axis-aligned RoIAlign has no `aligned` argument: the box kernels never shift by half a pixel.
+
+int mvr_roi_align_2d_forward(const void* input, const void* rois, void* output, int dtype, int64_t N, int64_t C,
+                             int64_t H, int64_t W, int64_t R, int roi_width, int oh, int ow, float spatial_scale,
+                             int sampling_ratio, int order, int* status, void* stream) {
+  return mvr_roi_resample_fwd(input, rois, output, dtype, 2, MVR_ROI_BOX, N, C, 1, H, W, R, roi_width, 1, oh, ow,
+                              spatial_scale, sampling_ratio, 0, order, status, stream);
+}
+int mvr_roi_align_2d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype, int64_t N,
+                              int64_t C, int64_t H, int64_t W, int64_t R, int roi_width, int oh, int ow,
+                              float spatial_scale, int sampling_ratio, int order, int* status, void* stream) {
+  return mvr_roi_resample_bwd(top_grad, rois, bottom_grad, dtype, 2, MVR_ROI_BOX, N, C, 1, H, W, R, roi_width, 1, oh,
+                              ow, spatial_scale, sampling_ratio, 0, order, status, stream);
+}
+int mvr_roi_align_3d_forward(const void* input, const void* rois, void* output, int dtype, int64_t N, int64_t C,
+                             int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh, int ow,
+                             float spatial_scale, int sampling_ratio, int order, int* status, void* stream) {
+  return mvr_roi_resample_fwd(input, rois, output, dtype, 3, MVR_ROI_BOX, N, C, D, H, W, R, roi_width, od, oh, ow,
+                              spatial_scale, sampling_ratio, 0, order, status, stream);
+}
+int mvr_roi_align_3d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype, int64_t N,
+                              int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh,
+                              int ow, float spatial_scale, int sampling_ratio, int order, int* status, void* stream) {
+  return mvr_roi_resample_bwd(top_grad, rois, bottom_grad, dtype, 3, MVR_ROI_BOX, N, C, D, H, W, R, roi_width, od, oh,
+                              ow, spatial_scale, sampling_ratio, 0, order, status, stream);
+}
+int mvr_roi_align_rotated_2d_forward(const void* input, const void* rois, void* output, int dtype, int64_t N,
+                                     int64_t C, int64_t H, int64_t W, int64_t R, int roi_width, int oh, int ow,
+                                     float spatial_scale, int sampling_ratio, int aligned, int order, int* status,
+                                     void* stream) {
+  return mvr_roi_resample_fwd(input, rois, output, dtype, 2, MVR_ROI_ROTATED, N, C, 1, H, W, R, roi_width, 1, oh, ow,
+                              spatial_scale, sampling_ratio, aligned, order, status, stream);
+}
+int mvr_roi_align_rotated_2d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype, int64_t N,
+                                      int64_t C, int64_t H, int64_t W, int64_t R, int roi_width, int oh, int ow,
+                                      float spatial_scale, int sampling_ratio, int aligned, int order, int* status,
+                                      void* stream) {
+  return mvr_roi_resample_bwd(top_grad, rois, bottom_grad, dtype, 2, MVR_ROI_ROTATED, N, C, 1, H, W, R, roi_width, 1,
+                              oh, ow, spatial_scale, sampling_ratio, aligned, order, status, stream);
+}
+int mvr_roi_align_rotated_3d_forward(const void* input, const void* rois, void* output, int dtype, int64_t N,
+                                     int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od,
+                                     int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                                     int* status, void* stream) {
+  return mvr_roi_resample_fwd(input, rois, output, dtype, 3, MVR_ROI_ROTATED, N, C, D, H, W, R, roi_width, od, oh, ow,
+                              spatial_scale, sampling_ratio, aligned, order, status, stream);
+}
+int mvr_roi_align_rotated_3d_backward(const void* top_grad, const void* rois, void* bottom_grad, int dtype, int64_t N,
+                                      int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od,
+                                      int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                                      int* status, void* stream) {
+  return mvr_roi_resample_bwd(top_grad, rois, bottom_grad, dtype, 3, MVR_ROI_ROTATED, N, C, D, H, W, R, roi_width, od,
+                              oh, ow, spatial_scale, sampling_ratio, aligned, order, status, stream);
+}
+int mvr_affine_2d(const void* input, const void* rois, void* output, int dtype, int64_t N, int64_t C, int64_t H,
+                  int64_t W, int64_t R, int roi_width, int oh, int ow, float spatial_scale, int sampling_ratio,
+                  int aligned, int order, int* status, void* stream) {
+  return mvr_roi_resample_fwd(input, rois, output, dtype, 2, MVR_ROI_ROTATED, N, C, 1, H, W, R, roi_width, 1, oh, ow,
+                              spatial_scale, sampling_ratio, aligned, order, status, stream);
+}
+int mvr_affine_3d(const void* input, const void* rois, void* output, int dtype, int64_t N, int64_t C, int64_t D,
+                  int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh, int ow, float spatial_scale,
+                  int sampling_ratio, int aligned, int order, int* status, void* stream) {
+  return mvr_roi_resample_fwd(input, rois, output, dtype, 3, MVR_ROI_ROTATED, N, C, D, H, W, R, roi_width, od, oh, ow,
+                              spatial_scale, sampling_ratio, aligned, order, status, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,287 @@
+// Roi decode, sample lattice and interpolation taps of the resampling path, written once
+// for every element type (see mvr_arith.cuh for why each step is a separately rounded
+// operation).  Follows
+//   roi decode + lattice   medvision/csrc/cuda/roi_align_{2d,3d}_cuda_kernel.cuh:26-69,
+//                          medvision/csrc/cuda/roi_align_rotated_{2d,3d}_cuda_kernel.cuh:30-103
+//   taps                   medvision/csrc/cuda/interpolation_helpers_{2d,3d}.h
+#pragma once
+#include "mvr_arith.cuh"
+
+namespace mvr {
+
+enum { KIND_BOX = 0, KIND_ROTATED = 1 };
+
+// Geometry of one roi, decoded once per CTA.  Axis index 0 = x (w), 1 = y (h), 2 = z (d).
+template <typename T>
+struct RoiGeom {
+  int batch;
+  int grid[3];
+  T start[3];   // box: roi start in the volume; rotated: -size/2 in the roi frame
+  T bin[3];
+  T centre[3];  // rotated only
+  T rot[9];     // rotated 3D: R11..R33 (row major); rotated 2D: rot[0] = cos, rot[1] = sin
+  T count_fwd, count_bwd;
+};
+
+template <typename T>
+__device__ __forceinline__ T rot_entry(T a, T b, T c, T d, T e, bool minus, int mode_) {
+  typedef Ar<T> A;
+  const T ab = A::mul(a, b);
+  const T de = A::mul(d, e);
+  const int mode = A::kCanFuse ? mode_ : 0;
+  if (mode == 1) return A::fma_(ab, c, minus ? A::neg(de) : de);
+  const T abc = A::mul(ab, c);
+  if (mode == 2) return A::fma_(minus ? A::neg(d) : d, e, abc);
+  return minus ? A::sub(abc, de) : A::add(abc, de);
+}
+
+// osz = {ow, oh, od}
+template <typename T>
+__device__ void decode_roi(const T* __restrict__ rois, long long n, int ndim, int kind, const int* osz,
+                           float spatial_scale, int sampling_ratio, int aligned, int fm, RoiGeom<T>& g) {
+  typedef Ar<T> A;
+  const int width = (kind == KIND_BOX) ? (ndim == 2 ? 5 : 7) : (ndim == 2 ? 6 : 10);
+  const T scale = A::ff(spatial_scale);
+  const T one = A::fi(1);
+  T r[10];
+  for (int k = 0; k < width; ++k) r[k] = rois[n * width + k];
+  g.batch = A::toi(r[0]);
+  T size[3];
+  if (kind == KIND_BOX) {
+    for (int a = 0; a < ndim; ++a) {
+      const T s = A::mul(r[1 + a], scale);
+      const T e = A::mul(r[1 + ndim + a], scale);
+      T sz = (A::kCanFuse && Fm::boxsize(fm)) ? A::fma_(r[1 + ndim + a], scale, A::neg(s)) : A::sub(e, s);
+      if (!A::ge_one(sz)) sz = one;  // max(size, 1); a NaN size becomes 1 (fmax)
+      g.start[a] = s;
+      size[a] = sz;
+      g.centre[a] = A::fi(0);
+    }
+  } else {
+    const T off = aligned ? A::ff(0.5f) : A::fi(0);
+    for (int a = 0; a < ndim; ++a) {
+      if (A::kCanFuse && Fm::centre(fm)) g.centre[a] = A::fma_(r[1 + a], scale, A::neg(off));
+      else g.centre[a] = A::sub(A::mul(r[1 + a], scale), off);
+      T sz = A::mul(r[1 + ndim + a], scale);
+      if (!aligned && !A::ge_one(sz)) sz = one;
+      size[a] = sz;
+    }
+    if (ndim == 2) {
+      g.rot[0] = A::cosT(r[5]);
+      g.rot[1] = A::sinT(r[5]);
+    } else {
+      const T cg = A::cosT(r[7]), sg = A::sinT(r[7]);
+      const T cb = A::cosT(r[8]), sb = A::sinT(r[8]);
+      const T ca = A::cosT(r[9]), sa = A::sinT(r[9]);
+      g.rot[0] = A::mul(ca, cb);
+      g.rot[1] = rot_entry<T>(ca, sb, sg, sa, cg, true, Fm::entry(fm, 0));
+      g.rot[2] = rot_entry<T>(ca, sb, cg, sa, sg, false, Fm::entry(fm, 1));
+      g.rot[3] = A::mul(sa, cb);
+      g.rot[4] = rot_entry<T>(sa, sb, sg, ca, cg, false, Fm::entry(fm, 2));
+      g.rot[5] = rot_entry<T>(sa, sb, cg, ca, sg, true, Fm::entry(fm, 3));
+      g.rot[6] = A::neg(sb);
+      g.rot[7] = A::mul(cb, sg);
+      g.rot[8] = A::mul(cb, cg);
+    }
+  }
+  int prod = 1;
+  for (int a = 0; a < ndim; ++a) {
+    const T o = A::fi(osz[a]);
+    g.bin[a] = A::div(size[a], o);
+    if (sampling_ratio > 0) {
+      g.grid[a] = sampling_ratio;
+    } else {
+      const float cq = A::tof(A::ceilT(A::div(size[a], o)));
+      g.grid[a] = (cq == cq && fabsf(cq) < 2e9f) ? (int)cq : 0;
+    }
+    if (kind == KIND_ROTATED) g.start[a] = A::halve_neg(size[a]);
+    prod *= g.grid[a];
+  }
+  for (int a = ndim; a < 3; ++a) {
+    g.grid[a] = 1;
+    g.start[a] = g.bin[a] = g.centre[a] = A::fi(0);
+  }
+  g.count_fwd = A::fi(max(prod, 1));
+  // the 2D backward kernels divide by the plain product, the 3D ones by max(product, 1)
+  g.count_bwd = (ndim == 2) ? A::fi(prod) : A::fi(max(prod, 1));
+}
+
+// in-bin offset of sub-sample i:  ((i + .5) * bin) / g
+template <typename T>
+__device__ __forceinline__ T lattice_sub(T bin, int i, int g) {
+  typedef Ar<T> A;
+  return A::div(A::mul(A::ff((float)i + .5f), bin), A::fi(g));
+}
+
+// start + p*bin
+template <typename T>
+__device__ __forceinline__ T lattice_base(T start, int p, T bin, int fm) {
+  typedef Ar<T> A;
+  if (A::kCanFuse && Fm::lattice(fm)) return A::fma_(A::fi(p), bin, start);
+  return A::add(start, A::mul(A::fi(p), bin));
+}
+
+// ((a1*x + a2*y) + a3*z) + c
+template <typename T>
+__device__ __forceinline__ T rot_row3(T a1, T x, T a2, T y, T a3, T z, T c, int mode_) {
+  typedef Ar<T> A;
+  const int mode = A::kCanFuse ? mode_ : 0;
+  T t;
+  switch (mode) {
+    case 1: t = A::add(A::fma_(a1, x, A::mul(a2, y)), A::mul(a3, z)); break;
+    case 2: t = A::fma_(a3, z, A::fma_(a1, x, A::mul(a2, y))); break;
+    case 3: t = A::add(A::fma_(a2, y, A::mul(a1, x)), A::mul(a3, z)); break;
+    case 4: t = A::fma_(a3, z, A::fma_(a2, y, A::mul(a1, x))); break;
+    case 5: t = A::fma_(a3, z, A::add(A::mul(a1, x), A::mul(a2, y))); break;
+    default: t = A::add(A::add(A::mul(a1, x), A::mul(a2, y)), A::mul(a3, z)); break;
+  }
+  return A::add(t, c);
+}
+
+// (x*a -/+ y*b) + c
+template <typename T>
+__device__ __forceinline__ T rot_row2(T x, T a, T y, T b, bool minus, T c, int fm) {
+  typedef Ar<T> A;
+  const int mode = A::kCanFuse ? Fm::rot2(fm) : 0;
+  T t;
+  if (mode == 1) {
+    const T yb = A::mul(y, b);
+    t = A::fma_(x, a, minus ? A::neg(yb) : yb);
+  } else if (mode == 2) {
+    t = A::fma_(minus ? A::neg(y) : y, b, A::mul(x, a));
+  } else {
+    t = minus ? A::sub(A::mul(x, a), A::mul(y, b)) : A::add(A::mul(x, a), A::mul(y, b));
+  }
+  return A::add(t, c);
+}
+
+// One axis of the interpolation helpers: clamp to >= 0, truncate, neighbour, low/high weight.
+template <typename T>
+struct AxisTap {
+  int i0, i1;
+  T l, h;
+};
+
+template <typename T>
+__device__ __forceinline__ bool axis_outside(T c, int size) {
+  const float f = Ar<T>::tof(c);  // exact for half; float compare equals the reference's for float
+  return (f < -1.0f) || (f > (float)size);
+}
+template <>
+__device__ __forceinline__ bool axis_outside<double>(double c, int size) {
+  return (c < -1.0) || (c > (double)size);
+}
+
+template <typename T>
+__device__ __forceinline__ void axis_tap(T c, int size, AxisTap<T>& t) {
+  typedef Ar<T> A;
+  if (A::le_zero(c)) c = A::fi(0);
+  int i0 = A::toi(c);
+  int i1;
+  if (i0 >= size - 1) {
+    i1 = i0 = size - 1;
+    c = A::fi(i0);
+  } else {
+    i1 = i0 + 1;
+  }
+  t.i0 = i0;
+  t.i1 = i1;
+  t.l = A::sub(c, A::fi(i0));
+  t.h = A::sub(A::fi(1), t.l);  // equals the reference's double-precision 1. - l rounded once
+}
+
+template <typename T>
+__device__ __forceinline__ void nearest_pick(const AxisTap<T>* t, int ndim, T* w) {
+  typedef Ar<T> A;
+  const int nt = 1 << ndim;
+  for (int k = 0; k < nt; ++k) w[k] = A::fi(0);
+  // first tap, in the reference's order, whose per-axis weights are all >= 0.5
+  for (int k = 0; k < nt; ++k) {
+    bool ok = true;
+    for (int a = 0; a < ndim; ++a) {
+      // tap k uses the high weight of axis a when the corresponding bit is clear;
+      // bit order: x is the lowest bit, then y, then z
+      const bool low = (k >> a) & 1;
+      ok = ok && A::ge_half(low ? t[a].l : t[a].h);
+    }
+    if (ok) {
+      w[k] = A::fi(1);
+      break;
+    }
+  }
+}
+
+// Weights and flat element offsets of the 2^ndim taps of a sample at (z, y, x).
+// Returns false when the sample lies outside the [-1, size] band: value 0, no gradient.
+// Tap order: k bit0 = x1, bit1 = y1, bit2 = z1 (the reference's w1..w8 / v1..v8 order).
+template <typename T, int NDIM>
+__device__ __forceinline__ bool make_taps(int D, int H, int W, T z, T y, T x, int order, T* w, long long* off) {
+  typedef Ar<T> A;
+  AxisTap<T> t[3];
+  if (axis_outside<T>(y, H) || axis_outside<T>(x, W)) return false;
+  if (NDIM == 3 && axis_outside<T>(z, D)) return false;
+  axis_tap<T>(x, W, t[0]);
+  axis_tap<T>(y, H, t[1]);
+  if (NDIM == 3) axis_tap<T>(z, D, t[2]);
+  if (NDIM == 2) {
+    off[0] = (long long)t[1].i0 * W + t[0].i0;
+    off[1] = (long long)t[1].i0 * W + t[0].i1;
+    off[2] = (long long)t[1].i1 * W + t[0].i0;
+    off[3] = (long long)t[1].i1 * W + t[0].i1;
+    if (order == 0) {
+      nearest_pick<T>(t, 2, w);
+    } else {
+      w[0] = A::mul(t[1].h, t[0].h);
+      w[1] = A::mul(t[1].h, t[0].l);
+      w[2] = A::mul(t[1].l, t[0].h);
+      w[3] = A::mul(t[1].l, t[0].l);
+    }
+  } else {
+    const long long HW = (long long)H * W;
+    const long long z0 = t[2].i0 * HW, z1 = t[2].i1 * HW;
+    const long long y0 = (long long)t[1].i0 * W, y1 = (long long)t[1].i1 * W;
+    off[0] = z0 + y0 + t[0].i0;
+    off[1] = z0 + y0 + t[0].i1;
+    off[2] = z0 + y1 + t[0].i0;
+    off[3] = z0 + y1 + t[0].i1;
+    off[4] = z1 + y0 + t[0].i0;
+    off[5] = z1 + y0 + t[0].i1;
+    off[6] = z1 + y1 + t[0].i0;
+    off[7] = z1 + y1 + t[0].i1;
+    if (order == 0) {
+      nearest_pick<T>(t, 3, w);
+    } else {
+      const T hzhy = A::mul(t[2].h, t[1].h), hzly = A::mul(t[2].h, t[1].l);
+      const T lzhy = A::mul(t[2].l, t[1].h), lzly = A::mul(t[2].l, t[1].l);
+      w[0] = A::mul(hzhy, t[0].h);
+      w[1] = A::mul(hzhy, t[0].l);
+      w[2] = A::mul(hzly, t[0].h);
+      w[3] = A::mul(hzly, t[0].l);
+      w[4] = A::mul(lzhy, t[0].h);
+      w[5] = A::mul(lzhy, t[0].l);
+      w[6] = A::mul(lzly, t[0].h);
+      w[7] = A::mul(lzly, t[0].l);
+    }
+  }
+  return true;
+}
+
+// w1*v1 + w2*v2 + ... summed left to right.
+template <typename T, int NT>
+__device__ __forceinline__ T tap_sum(const T* w, const T* v, int fm) {
+  typedef Ar<T> A;
+  T acc;
+  const int mode = A::kCanFuse ? Fm::tap(fm) : 0;
+  if (mode) {
+    acc = (mode == 1) ? A::fma_(w[0], v[0], A::mul(w[1], v[1])) : A::fma_(w[1], v[1], A::mul(w[0], v[0]));
+#pragma unroll
+    for (int k = 2; k < NT; ++k) acc = A::fma_(w[k], v[k], acc);
+    return acc;
+  }
+  acc = A::mul(w[0], v[0]);
+#pragma unroll
+  for (int k = 1; k < NT; ++k) acc = A::add(acc, A::mul(w[k], v[k]));
+  return acc;
+}
+
+}  // namespace mvr

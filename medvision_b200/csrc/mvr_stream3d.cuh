@@ -1,0 +1,386 @@
+// Streaming forward kernel for dense 3D resampling: one sample per output voxel
+// (sampling_ratio == 1), half or float, rotated rois (RoIAlignRotated 3D / affine_3d) and
+// axis-aligned boxes (RoIAlign 3D).  This is the shape of every batched augmentation call
+// (Resize, RandomAffine/Scale/Shift/Rotate, CropRandomWithAffine:
+// medvision/aug_cuda_batch/aug_spatial.py:118-155,404-446,674-715), where the output has
+// millions of voxels per roi and the work is a stream over the volume.
+//
+// Layout of the work
+//   * CTA = 256 threads = a 32 (w) x 16 (h) tile of output positions x a chunk of output depth
+//     of ONE (roi, channel).  A thread owns two w-adjacent voxels and walks the depth chunk,
+//     so output stores are 2-element vectors, contiguous along w within a warp row.
+//   * The roi is decoded (incl. its six sin/cos) once per CTA; per-depth quantities are
+//     tabulated once per CTA in shared memory.
+//   * Every arithmetic step keeps the reference's rounding sequence (mvr_arith.cuh); what is
+//     removed is only work whose result is provably identical:
+//       - z-separable rois (no rotation, or rotation about z only -- the only rotation the
+//         augmentations use): R13 = R23 = R31 = R32 = 0 and R33 = 1 exactly, so the in-plane
+//         sample position, its four in-plane tap offsets and weights depend on (h, w) only and
+//         are computed once per thread; the z tap (planes, weights) depends on depth only and
+//         is tabulated per CTA.  Adding a*0 or multiplying by 1 never changes a finite value.
+//       - consecutive output depths usually share a source plane (z1 of one = z0 of the next):
+//         its four tap values stay in registers instead of being reloaded.
+//       - general rotations: the products R_i2*y, R_i1*x (per thread) and R_i3*z (per depth)
+//         are formed once; they are separately rounded values in the reference as well
+//         (half: every product is rounded; float: see the contraction pattern).
+//   * Half math runs on both lanes of half2 instructions (the two voxels of a thread).
+//
+// Gathers go through L1/L2 (__ldg): neighbouring threads and consecutive depths hit the same
+// lines, and the per-thread register reuse above removes about half of the loads outright.
+#pragma once
+#include "mvr_generic.cuh"
+
+namespace mvr {
+
+constexpr int MVR_STREAM3D_NOT_APPLICABLE = 1;
+
+constexpr int kS3Threads = 256;
+constexpr int kS3TileW = 32;   // output voxels along w per CTA (2 per thread)
+constexpr int kS3TileH = 16;
+constexpr int kS3MaxChunk = 64;  // output depths per CTA
+
+// The float contraction pattern this kernel hard-codes (the reference build's).
+constexpr int kS3FloatPattern = kReferenceContraction;
+
+// ---- two-lane arithmetic: lane a = voxel at w, lane b = voxel at w+1 -----------------------
+template <typename T> struct P2;
+
+template <> struct P2<__half> {
+  typedef __half2 V;
+  __device__ __forceinline__ static V make(__half a, __half b) { return __halves2half2(a, b); }
+  __device__ __forceinline__ static V dup(__half a) { return __half2half2(a); }
+  __device__ __forceinline__ static V add(V a, V b) { return __hadd2_rn(a, b); }
+  __device__ __forceinline__ static V mul(V a, V b) { return __hmul2_rn(a, b); }
+  // a1*x + py : both roundings kept
+  __device__ __forceinline__ static V row_xy(V a1, V x, V py) { return __hadd2_rn(__hmul2_rn(a1, x), py); }
+  __device__ __forceinline__ static V tap_first(V w0, V v0, V w1, V v1) {
+    return __hadd2_rn(__hmul2_rn(w0, v0), __hmul2_rn(w1, v1));
+  }
+  __device__ __forceinline__ static V tap_next(V acc, V w, V v) { return __hadd2_rn(acc, __hmul2_rn(w, v)); }
+  __device__ __forceinline__ static __half lo(V v) { return __low2half(v); }
+  __device__ __forceinline__ static __half hi(V v) { return __high2half(v); }
+  __device__ __forceinline__ static V select(V v, bool keep_a, bool keep_b) {
+    unsigned u = *reinterpret_cast<unsigned*>(&v);
+    u &= (keep_a ? 0x0000ffffu : 0u) | (keep_b ? 0xffff0000u : 0u);
+    return *reinterpret_cast<V*>(&u);
+  }
+  __device__ __forceinline__ static void store2(__half* p, V v) { *reinterpret_cast<__half2*>(p) = v; }
+};
+
+struct Float2Lanes { float a, b; };
+template <> struct P2<float> {
+  typedef Float2Lanes V;
+  __device__ __forceinline__ static V make(float a, float b) { V v; v.a = a; v.b = b; return v; }
+  __device__ __forceinline__ static V dup(float a) { return make(a, a); }
+  __device__ __forceinline__ static V add(V a, V b) { return make(__fadd_rn(a.a, b.a), __fadd_rn(a.b, b.b)); }
+  __device__ __forceinline__ static V mul(V a, V b) { return make(__fmul_rn(a.a, b.a), __fmul_rn(a.b, b.b)); }
+  // fma(a1, x, py): the x product is the fused one in the reference build
+  __device__ __forceinline__ static V row_xy(V a1, V x, V py) {
+    return make(__fmaf_rn(a1.a, x.a, py.a), __fmaf_rn(a1.b, x.b, py.b));
+  }
+  __device__ __forceinline__ static V tap_first(V w0, V v0, V w1, V v1) {
+    return make(__fmaf_rn(w0.a, v0.a, __fmul_rn(w1.a, v1.a)), __fmaf_rn(w0.b, v0.b, __fmul_rn(w1.b, v1.b)));
+  }
+  __device__ __forceinline__ static V tap_next(V acc, V w, V v) {
+    return make(__fmaf_rn(w.a, v.a, acc.a), __fmaf_rn(w.b, v.b, acc.b));
+  }
+  __device__ __forceinline__ static float lo(V v) { return v.a; }
+  __device__ __forceinline__ static float hi(V v) { return v.b; }
+  __device__ __forceinline__ static V select(V v, bool keep_a, bool keep_b) {
+    return make(keep_a ? v.a : 0.0f, keep_b ? v.b : 0.0f);
+  }
+  __device__ __forceinline__ static void store2(float* p, V v) { *reinterpret_cast<float2*>(p) = make_float2(v.a, v.b); }
+};
+
+// per-axis (l, h) of one sample; order 0 replaces them by the one-hot choice that the
+// reference's first-match rule makes on this axis (prefer the low index when h >= .5)
+template <typename T>
+__device__ __forceinline__ void nearest_axis(T& l, T& h) {
+  typedef Ar<T> A;
+  const bool hh = A::ge_half(h), ll = A::ge_half(l);
+  h = hh ? A::fi(1) : A::fi(0);
+  l = (!hh && ll) ? A::fi(1) : A::fi(0);
+}
+
+template <typename T>
+struct S3ZTap {        // z-separable: per output depth
+  long long o0, o1;    // element offsets of the two source planes inside the volume
+  T l, h;
+  int inside;
+};
+template <typename T>
+struct S3ZProd {       // general rotation: per output depth, the rounded products R_i3 * z
+  T p[3];
+};
+
+template <typename T>
+struct S3Shared {
+  RoiGeom<T> g;
+  int zsep;            // 1: z-separable path
+  union {
+    S3ZTap<T> zt[kS3MaxChunk];
+    S3ZProd<T> zp[kS3MaxChunk];
+  };
+};
+
+struct S3Launch {
+  int tiles_w, tiles_h, chunks, chunk;  // chunk = output depths per CTA
+  int vec_store;                        // 1: two-element vector stores are aligned
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kS3Threads)
+resample_fwd_stream3d(const Params p, const S3Launch L) {
+  typedef Ar<T> A;
+  typedef P2<T> Q;
+  typedef typename Q::V V;
+  __shared__ S3Shared<T> sh;
+
+  // ---- CTA coordinates: tile_w fastest, then tile_h, chunk, (roi, channel)
+  long long cta = blockIdx.x;
+  const int tw = (int)(cta % L.tiles_w); cta /= L.tiles_w;
+  const int th = (int)(cta % L.tiles_h); cta /= L.tiles_h;
+  const int ck = (int)(cta % L.chunks);  cta /= L.chunks;
+  const long long nc = cta;
+  const long long n = nc / p.C;
+  const int c = (int)(nc % p.C);
+  const int pd0 = ck * L.chunk;
+  const int npd = min(L.chunk, p.od - pd0);
+
+  const int fm = kS3FloatPattern;
+  if (threadIdx.x == 0) {
+    const int osz[3] = {p.ow, p.oh, p.od};
+    decode_roi<T>((const T*)p.rois, n, 3, p.kind, osz, p.spatial_scale, 1, p.aligned, fm, sh.g);
+    const RoiGeom<T>& g = sh.g;
+    int zsep = 1;
+    if (p.kind == KIND_ROTATED) {
+      const float one = 1.0f;
+      zsep = (A::tof(g.rot[2]) == 0.0f) && (A::tof(g.rot[5]) == 0.0f) && (A::tof(g.rot[6]) == 0.0f) &&
+             (A::tof(g.rot[7]) == 0.0f) && (A::tof(g.rot[8]) == one);
+    }
+    // the shortcut drops terms of the form 0*coordinate: every lattice coordinate must be finite
+    const int last[3] = {p.ow - 1, p.oh - 1, p.od - 1};
+    for (int a = 0; a < 3; ++a) {
+      const T sub = lattice_sub<T>(g.bin[a], 0, 1);
+      const T c0 = A::add(lattice_base<T>(g.start[a], 0, g.bin[a], fm), sub);
+      const T c1 = A::add(lattice_base<T>(g.start[a], last[a], g.bin[a], fm), sub);
+      zsep = zsep && A::finite(c0) && A::finite(c1) && A::finite(g.centre[a]);
+    }
+    sh.zsep = zsep;
+  }
+  __syncthreads();
+  const RoiGeom<T>& g = sh.g;
+  const bool zsep = sh.zsep != 0;
+  const bool rotated = (p.kind == KIND_ROTATED);
+  const bool bad_batch = (g.batch < 0 || g.batch >= p.N);
+  const long long HW = (long long)p.H * p.W;
+
+  // ---- per-depth table
+  if (!bad_batch && (int)threadIdx.x < npd) {
+    const int i = threadIdx.x;
+    const T z = A::add(lattice_base<T>(g.start[2], pd0 + i, g.bin[2], fm), lattice_sub<T>(g.bin[2], 0, 1));
+    if (zsep) {
+      const T rz = rotated ? A::add(z, g.centre[2]) : z;
+      S3ZTap<T> e;
+      e.inside = !axis_outside<T>(rz, p.D);
+      AxisTap<T> t;
+      axis_tap<T>(rz, p.D, t);
+      if (p.order == 0) nearest_axis<T>(t.l, t.h);
+      e.o0 = t.i0 * HW;
+      e.o1 = t.i1 * HW;
+      e.l = t.l;
+      e.h = t.h;
+      sh.zt[i] = e;
+    } else {
+      S3ZProd<T> e;
+      e.p[0] = A::mul(g.rot[2], z);
+      e.p[1] = A::mul(g.rot[5], z);
+      e.p[2] = A::mul(g.rot[8], z);
+      sh.zp[i] = e;
+    }
+  }
+  __syncthreads();
+
+  // ---- this thread's two output columns
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pw0 = tw * kS3TileW + (warp & 1) * 16 + (lane & 7) * 2;
+  const int ph = th * kS3TileH + (warp >> 1) * 4 + (lane >> 3);
+  if (ph >= p.oh || pw0 >= p.ow) return;
+  const bool has_b = (pw0 + 1 < p.ow);
+  const long long plane_o = (long long)p.oh * p.ow;
+  T* out = (T*)p.out + nc * p.ovol + (long long)pd0 * plane_o + (long long)ph * p.ow + pw0;
+  const bool vec = L.vec_store && has_b;
+
+  if (bad_batch) {
+    if (p.status && threadIdx.x == 0 && tw == 0 && th == 0 && ck == 0) atomicOr(p.status, STATUS_BAD_BATCH_INDEX);
+    for (int i = 0; i < npd; ++i) {
+      out[i * plane_o] = A::fi(0);
+      if (has_b) out[i * plane_o + 1] = A::fi(0);
+    }
+    return;
+  }
+  const T* vol = (const T*)p.in + ((long long)g.batch * p.C + c) * p.vol;
+  const V zero2 = Q::dup(A::fi(0));
+
+  // lattice coordinates of the two voxels in the roi frame
+  const T sub_x = lattice_sub<T>(g.bin[0], 0, 1), sub_y = lattice_sub<T>(g.bin[1], 0, 1);
+  const T xa = A::add(lattice_base<T>(g.start[0], pw0, g.bin[0], fm), sub_x);
+  const T xb = A::add(lattice_base<T>(g.start[0], has_b ? pw0 + 1 : pw0, g.bin[0], fm), sub_x);
+  const T y = A::add(lattice_base<T>(g.start[1], ph, g.bin[1], fm), sub_y);
+  const V x2 = Q::make(xa, xb);
+
+  if (zsep) {
+    // ---- in-plane position, taps and weights: once per thread
+    V rx2, ry2;
+    if (rotated) {
+      rx2 = Q::add(Q::row_xy(Q::dup(g.rot[0]), x2, Q::dup(A::mul(g.rot[1], y))), Q::dup(g.centre[0]));
+      ry2 = Q::add(Q::row_xy(Q::dup(g.rot[3]), x2, Q::dup(A::mul(g.rot[4], y))), Q::dup(g.centre[1]));
+    } else {
+      rx2 = x2;
+      ry2 = Q::dup(y);
+    }
+    const T rx[2] = {Q::lo(rx2), Q::hi(rx2)}, ry[2] = {Q::lo(ry2), Q::hi(ry2)};
+    int o00[2], o01[2], o10[2], o11[2];
+    T lx[2], hx[2], ly[2], hy[2];
+    bool in[2];
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      in[v] = !(axis_outside<T>(ry[v], p.H) || axis_outside<T>(rx[v], p.W));
+      AxisTap<T> tx, ty;
+      axis_tap<T>(rx[v], p.W, tx);
+      axis_tap<T>(ry[v], p.H, ty);
+      if (p.order == 0) { nearest_axis<T>(tx.l, tx.h); nearest_axis<T>(ty.l, ty.h); }
+      o00[v] = ty.i0 * p.W + tx.i0;
+      o01[v] = ty.i0 * p.W + tx.i1;
+      o10[v] = ty.i1 * p.W + tx.i0;
+      o11[v] = ty.i1 * p.W + tx.i1;
+      lx[v] = tx.l; hx[v] = tx.h; ly[v] = ty.l; hy[v] = ty.h;
+    }
+    in[1] = in[1] && has_b;
+    const V lx2 = Q::make(lx[0], lx[1]), hx2 = Q::make(hx[0], hx[1]);
+    const V ly2 = Q::make(ly[0], ly[1]), hy2 = Q::make(hy[0], hy[1]);
+
+    V q0[4], q1[4];          // tap values of the two source planes, lanes = the two voxels
+    long long have1 = -1;    // plane offset whose values sit in q1
+    for (int i = 0; i < npd; ++i) {
+      const S3ZTap<T> e = sh.zt[i];
+      V val = zero2;
+      if (e.inside) {
+        if (e.o0 == have1) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) q0[k] = q1[k];
+        } else {
+          const T* pl = vol + e.o0;
+          q0[0] = Q::make(__ldg(pl + o00[0]), __ldg(pl + o00[1]));
+          q0[1] = Q::make(__ldg(pl + o01[0]), __ldg(pl + o01[1]));
+          q0[2] = Q::make(__ldg(pl + o10[0]), __ldg(pl + o10[1]));
+          q0[3] = Q::make(__ldg(pl + o11[0]), __ldg(pl + o11[1]));
+        }
+        if (e.o1 == e.o0) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) q1[k] = q0[k];
+        } else {
+          const T* pl = vol + e.o1;
+          q1[0] = Q::make(__ldg(pl + o00[0]), __ldg(pl + o00[1]));
+          q1[1] = Q::make(__ldg(pl + o01[0]), __ldg(pl + o01[1]));
+          q1[2] = Q::make(__ldg(pl + o10[0]), __ldg(pl + o10[1]));
+          q1[3] = Q::make(__ldg(pl + o11[0]), __ldg(pl + o11[1]));
+        }
+        have1 = e.o1;
+        const V hz2 = Q::dup(e.h), lz2 = Q::dup(e.l);
+        const V hzhy = Q::mul(hz2, hy2), hzly = Q::mul(hz2, ly2);
+        const V lzhy = Q::mul(lz2, hy2), lzly = Q::mul(lz2, ly2);
+        V acc = Q::tap_first(Q::mul(hzhy, hx2), q0[0], Q::mul(hzhy, lx2), q0[1]);
+        acc = Q::tap_next(acc, Q::mul(hzly, hx2), q0[2]);
+        acc = Q::tap_next(acc, Q::mul(hzly, lx2), q0[3]);
+        acc = Q::tap_next(acc, Q::mul(lzhy, hx2), q1[0]);
+        acc = Q::tap_next(acc, Q::mul(lzhy, lx2), q1[1]);
+        acc = Q::tap_next(acc, Q::mul(lzly, hx2), q1[2]);
+        acc = Q::tap_next(acc, Q::mul(lzly, lx2), q1[3]);
+        // output_val = 0 + val (normalises -0), then /count with count == 1
+        val = Q::select(Q::add(zero2, acc), in[0], in[1]);
+      }
+      T* o = out + i * plane_o;
+      if (vec) {
+        Q::store2(o, val);
+      } else {
+        o[0] = Q::lo(val);
+        if (has_b) o[1] = Q::hi(val);
+      }
+    }
+    return;
+  }
+
+  // ---- general rotation: positions change with depth; x- and y-products are formed once
+  V sxy[3];
+#pragma unroll
+  for (int r = 0; r < 3; ++r)
+    sxy[r] = Q::row_xy(Q::dup(g.rot[3 * r]), x2, Q::dup(A::mul(g.rot[3 * r + 1], y)));
+  const V c2[3] = {Q::dup(g.centre[0]), Q::dup(g.centre[1]), Q::dup(g.centre[2])};
+  for (int i = 0; i < npd; ++i) {
+    const S3ZProd<T> e = sh.zp[i];
+    const V rx2 = Q::add(Q::add(sxy[0], Q::dup(e.p[0])), c2[0]);
+    const V ry2 = Q::add(Q::add(sxy[1], Q::dup(e.p[1])), c2[1]);
+    const V rz2 = Q::add(Q::add(sxy[2], Q::dup(e.p[2])), c2[2]);
+    const T rx[2] = {Q::lo(rx2), Q::hi(rx2)}, ry[2] = {Q::lo(ry2), Q::hi(ry2)}, rz[2] = {Q::lo(rz2), Q::hi(rz2)};
+    T w[2][8], v[2][8];
+    bool in[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      long long off[8];
+      in[s] = make_taps<T, 3>(p.D, p.H, p.W, rz[s], ry[s], rx[s], p.order, w[s], off);
+      if (s == 1) in[s] = in[s] && has_b;
+      if (in[s]) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[s][k] = __ldg(vol + off[k]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { v[s][k] = A::fi(0); w[s][k] = A::fi(0); }
+      }
+    }
+    V acc = Q::tap_first(Q::make(w[0][0], w[1][0]), Q::make(v[0][0], v[1][0]),
+                         Q::make(w[0][1], w[1][1]), Q::make(v[0][1], v[1][1]));
+#pragma unroll
+    for (int k = 2; k < 8; ++k) acc = Q::tap_next(acc, Q::make(w[0][k], w[1][k]), Q::make(v[0][k], v[1][k]));
+    const V val = Q::select(Q::add(zero2, acc), in[0], in[1]);
+    T* o = out + i * plane_o;
+    if (vec) {
+      Q::store2(o, val);
+    } else {
+      o[0] = Q::lo(val);
+      if (has_b) o[1] = Q::hi(val);
+    }
+  }
+}
+
+// Picks the streaming kernel when the call has its shape; returns MVR_STREAM3D_NOT_APPLICABLE
+// otherwise (the caller then uses the general kernel).
+inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
+  if (p.ndim != 3 || p.sampling_ratio != 1) return MVR_STREAM3D_NOT_APPLICABLE;
+  if (dtype != 0 /*f32*/ && dtype != 1 /*f16*/) return MVR_STREAM3D_NOT_APPLICABLE;
+  if (dtype == 0 && p.fm != kS3FloatPattern) return MVR_STREAM3D_NOT_APPLICABLE;
+  // small outputs (detection heads) are better served one element per thread
+  if (p.ovol < 4096 || p.ow < 8) return MVR_STREAM3D_NOT_APPLICABLE;
+  if ((long long)p.H * p.W >= 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
+
+  S3Launch L;
+  L.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
+  L.tiles_h = (p.oh + kS3TileH - 1) / kS3TileH;
+  // depth chunk: long enough to amortise the per-thread set-up and to reuse planes, short
+  // enough to give every SM several CTAs
+  const long long per_depth_ctas = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
+  int chunk = kS3MaxChunk;
+  while (chunk > 8 && per_depth_ctas * ((p.od + chunk - 1) / chunk) < 148LL * 16) chunk >>= 1;
+  if (chunk > p.od) chunk = p.od;
+  L.chunk = chunk;
+  L.chunks = (p.od + chunk - 1) / chunk;
+  const size_t esz = dtype == 0 ? 4 : 2;
+  L.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % (2 * esz) == 0);
+  const long long ctas = per_depth_ctas * L.chunks;
+  if (ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
+  if (dtype == 0) resample_fwd_stream3d<float><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
+  else resample_fwd_stream3d<__half><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+}  // namespace mvr

@@ -1,0 +1,42 @@
+"""Forward-only resampling entry points used by the batched CUDA augmentations.
+
+Same signatures as ``affine_2d`` / ``affine_3d`` of medvision/ops/cuda_fun_tools.py:6-91.
+"""
+import torch
+
+from .. import _C
+from ._common import parse_output_size
+
+# order 3 (Catmull-Rom) of the reference's affine kernels is not part of this library yet
+_SUPPORTED_ORDERS = [0, 1]
+
+
+def _affine(ndim, features, rois, out_size, spatial_scale, sampling_ratio, aligned, order):
+    out = parse_output_size(out_size, ndim, name="out_size")
+    assert features.dtype in [torch.float32, torch.float16], \
+        f'input must be float16 or float32 but got {features.dtype}'
+    assert order in [0, 1, 3], f'order {order} is not supported!'
+    if order not in _SUPPORTED_ORDERS:
+        raise NotImplementedError(f"order {order} is not implemented by medvision_b200 (orders {_SUPPORTED_ORDERS} are)")
+    if order == 0:
+        # one sample per output voxel: averaging would blend labels
+        sampling_ratio = 1
+    assert features.dim() == ndim + 2
+    output = features.new_empty((rois.size(0), features.size(1)) + tuple(out))
+    # the rois take the dtype (and device) of the image, as rois.type(features.type()) does
+    rois = rois.to(device=features.device, dtype=features.dtype)
+    fn = _C.affine_2d if ndim == 2 else _C.affine_3d
+    fn(features, rois, output, *out, spatial_scale, sampling_ratio, aligned, order)
+    return output
+
+
+def affine_2d(features, rois, out_size, spatial_scale, sampling_ratio=0, aligned=True, order=1):
+    """Resample rotated rois of (N, C, H, W) ``features`` to (R, C, out_h, out_w).
+    rois: (R, 6) = (batch_index, center_x, center_y, w, h, angle)."""
+    return _affine(2, features, rois, out_size, spatial_scale, sampling_ratio, aligned, order)
+
+
+def affine_3d(features, rois, out_size, spatial_scale, sampling_ratio=0, aligned=True, order=1):
+    """Resample rotated rois of (N, C, D, H, W) ``features`` to (R, C, out_d, out_h, out_w).
+    rois: (R, 10) = (batch_index, center_x, center_y, center_z, w, h, d, angle_x, angle_y, angle_z)."""
+    return _affine(3, features, rois, out_size, spatial_scale, sampling_ratio, aligned, order)

@@ -141,14 +141,27 @@ template <> struct Arith<DT_F16> {
   static const bool can_fuse = false;
 };
 
-// Which float products the device compiler is assumed to have fused into the following
-// add.  Bits:
-//   1  sample lattice:   start + p*bin            -> fma(p, bin, start)
-//   2  rotation:         R_1*x + R_2*y (+ R_3*z)  -> fma chain, first product of the LAST pair rounded
-//   4  tap sum:          w1*v1 + w2*v2 + ...      -> fma chain
-//   8  roi centre:       roi*scale - offset       -> fma(roi, scale, -offset)
-//  16  rotation matrix:  a*b*c -/+ d*e            -> fma(a*b, c, -/+ d*e)
-//  32  in bit-2/bit-4 chains, the FIRST product is the fused one: fma(a, b, c*d) instead of fma(c, d, a*b)
+// Which float products the device compiler fused into the following add (half never fuses).
+//   bit  0      sample lattice  start + p*bin          0 plain | 1 fma(p, bin, start)
+//   bit  1      roi centre      roi*scale - offset     0 plain | 1 fma(roi, scale, -offset)
+//   bit  2      box size        end*scale - start      0 plain | 1 fma(end, scale, -start)
+//   bits 3-4    tap sum         w1*v1 + w2*v2 + ...    0 plain | 1 fma(w1,v1,w2*v2) then fma chain
+//                                                      | 2 fma(w2,v2,w1*v1) then fma chain
+//   bits 5-6    2D rotation     x*a -/+ y*b            0 plain | 1 fma(x,a,-/+(y*b)) | 2 fma(-/+y,b,x*a)
+//   bits 7-9, 10-12, 13-15   3D rotation rows 1..3   (a1*x + a2*y) + a3*z
+//                               0 plain | 1 fma(a1,x,a2*y) + a3*z | 2 fma(a3,z,fma(a1,x,a2*y))
+//                               | 3 fma(a2,y,a1*x) + a3*z | 4 fma(a3,z,fma(a2,y,a1*x)) | 5 fma(a3,z,a1*x + a2*y)
+//   bits 16-17, 18-19, 20-21, 22-23   rotation entries R12, R13, R22, R23   a*b*c -/+ d*e
+//                               0 plain | 1 fma(a*b,c,-/+(d*e)) | 2 fma(-/+d,e,(a*b)*c)
+struct Fm {
+  static int lattice(int fm) { return fm & 1; }
+  static int centre(int fm) { return (fm >> 1) & 1; }
+  static int boxsize(int fm) { return (fm >> 2) & 1; }
+  static int tap(int fm) { return (fm >> 3) & 3; }
+  static int rot2(int fm) { return (fm >> 5) & 3; }
+  static int row(int fm, int r) { return (fm >> (7 + 3 * r)) & 7; }
+  static int entry(int fm, int e) { return (fm >> (16 + 2 * e)) & 3; }
+};
 
 // ------------------------------------------------------------------ interpolation
 // One axis of interpolation_helpers_*: clamp, floor, neighbour and the low/high weights.
@@ -186,9 +199,10 @@ inline bool outside(typename A::T c, int size) {
 template <class A>
 inline typename A::T tap_sum(const typename A::T* w, const typename A::T* v, int n, int fma_mode) {
   typedef typename A::T T;
-  if (A::can_fuse && (fma_mode & 4)) {
+  const int mode = A::can_fuse ? Fm::tap(fma_mode) : 0;
+  if (mode) {
     T acc;
-    if (fma_mode & 32) acc = A::fma_(w[0], v[0], A::mul(w[1], v[1]));
+    if (mode == 1) acc = A::fma_(w[0], v[0], A::mul(w[1], v[1]));
     else acc = A::fma_(w[1], v[1], A::mul(w[0], v[0]));
     for (int k = 2; k < n; ++k) acc = A::fma_(w[k], v[k], acc);
     return acc;
@@ -288,25 +302,28 @@ struct RoiGeom {
 
 template <class A>
 inline typename A::T mad_centre(typename A::T r, typename A::T s, typename A::T off, int fma_mode) {
-  if (A::can_fuse && (fma_mode & 8)) return A::fma_(r, s, A::neg(off));
+  if (A::can_fuse && Fm::centre(fma_mode)) return A::fma_(r, s, A::neg(off));
   return A::sub(A::mul(r, s), off);
 }
 
 // a*b*c -/+ d*e of the rotation-matrix entries
 template <class A>
 inline typename A::T rot_entry(typename A::T a, typename A::T b, typename A::T c, typename A::T d,
-                               typename A::T e, bool minus, int fma_mode) {
+                               typename A::T e, bool minus, int mode_) {
   typedef typename A::T T;
   const T ab = A::mul(a, b);
   const T de = A::mul(d, e);
-  if (A::can_fuse && (fma_mode & 16)) return A::fma_(ab, c, minus ? A::neg(de) : de);
+  const int mode = A::can_fuse ? mode_ : 0;
+  if (mode == 1) return A::fma_(ab, c, minus ? A::neg(de) : de);
   const T abc = A::mul(ab, c);
+  if (mode == 2) return A::fma_(minus ? A::neg(d) : d, e, abc);
   return minus ? A::sub(abc, de) : A::add(abc, de);
 }
 
 template <class A>
 void decode_roi(const void* rois, int64_t n, int ndim, int kind, const int* osz /*w,h,d*/,
-                float spatial_scale_f, int sampling_ratio, int aligned, int fma_mode, RoiGeom<A>& g) {
+                float spatial_scale_f, int sampling_ratio, int aligned, int fma_mode, const void* trig,
+                RoiGeom<A>& g) {
   typedef typename A::T T;
   const int nax = ndim;
   const int width = (kind == KIND_BOX) ? (ndim == 2 ? 5 : 7) : (ndim == 2 ? 6 : 10);
@@ -319,7 +336,7 @@ void decode_roi(const void* rois, int64_t n, int ndim, int kind, const int* osz 
     for (int a = 0; a < nax; ++a) {
       const T s = A::mul(r[1 + a], scale);
       const T e = A::mul(r[1 + nax + a], scale);
-      T sz = A::sub(e, s);
+      T sz = (A::can_fuse && Fm::boxsize(fma_mode)) ? A::fma_(r[1 + nax + a], scale, A::neg(s)) : A::sub(e, s);
       if (!(sz >= (T)1)) sz = (T)1;  // max(sz, 1) as fmaxf: a NaN size becomes 1
       g.start[a] = s;
       size[a] = sz;
@@ -332,20 +349,22 @@ void decode_roi(const void* rois, int64_t n, int ndim, int kind, const int* osz 
       if (!aligned && !(sz >= (T)1)) sz = (T)1;
       size[a] = sz;
     }
+    // `trig` (optional): per roi, cos and sin of each angle as evaluated elsewhere (the device's
+    // sinf/cosf differ from the host's by an ulp for some arguments)
     if (ndim == 2) {
       const T th = r[5];
-      g.rot[0] = A::cosT(th);
-      g.rot[1] = A::sinT(th);
+      g.rot[0] = trig ? A::ld(trig, n * 2 + 0) : A::cosT(th);
+      g.rot[1] = trig ? A::ld(trig, n * 2 + 1) : A::sinT(th);
     } else {
-      const T cg = A::cosT(r[7]), sg = A::sinT(r[7]);
-      const T cb = A::cosT(r[8]), sb = A::sinT(r[8]);
-      const T ca = A::cosT(r[9]), sa = A::sinT(r[9]);
+      const T cg = trig ? A::ld(trig, n * 6 + 0) : A::cosT(r[7]), sg = trig ? A::ld(trig, n * 6 + 1) : A::sinT(r[7]);
+      const T cb = trig ? A::ld(trig, n * 6 + 2) : A::cosT(r[8]), sb = trig ? A::ld(trig, n * 6 + 3) : A::sinT(r[8]);
+      const T ca = trig ? A::ld(trig, n * 6 + 4) : A::cosT(r[9]), sa = trig ? A::ld(trig, n * 6 + 5) : A::sinT(r[9]);
       g.rot[0] = A::mul(ca, cb);
-      g.rot[1] = rot_entry<A>(ca, sb, sg, sa, cg, true, fma_mode);
-      g.rot[2] = rot_entry<A>(ca, sb, cg, sa, sg, false, fma_mode);
+      g.rot[1] = rot_entry<A>(ca, sb, sg, sa, cg, true, Fm::entry(fma_mode, 0));
+      g.rot[2] = rot_entry<A>(ca, sb, cg, sa, sg, false, Fm::entry(fma_mode, 1));
       g.rot[3] = A::mul(sa, cb);
-      g.rot[4] = rot_entry<A>(sa, sb, sg, ca, cg, false, fma_mode);
-      g.rot[5] = rot_entry<A>(sa, sb, cg, ca, sg, true, fma_mode);
+      g.rot[4] = rot_entry<A>(sa, sb, sg, ca, cg, false, Fm::entry(fma_mode, 2));
+      g.rot[5] = rot_entry<A>(sa, sb, cg, ca, sg, true, Fm::entry(fma_mode, 3));
       g.rot[6] = A::neg(sb);
       g.rot[7] = A::mul(cb, sg);
       g.rot[8] = A::mul(cb, cg);
@@ -377,25 +396,26 @@ inline typename A::T lattice(typename A::T start, int p, typename A::T bin, int 
   typedef typename A::T T;
   const T t = A::div(A::mul(A::ff((float)i + .5f), bin), A::fi(g));
   T base;
-  if (A::can_fuse && (fma_mode & 1)) base = A::fma_(A::fi(p), bin, start);
+  if (A::can_fuse && Fm::lattice(fma_mode)) base = A::fma_(A::fi(p), bin, start);
   else base = A::add(start, A::mul(A::fi(p), bin));
   return A::add(base, t);
 }
 
-// r = ((a1*x + a2*y) [+ a3*z]) + c   with optional contraction
+// r = ((a1*x + a2*y) + a3*z) + c   with optional contraction
 template <class A>
 inline typename A::T rot_row3(typename A::T a1, typename A::T x, typename A::T a2, typename A::T y,
-                              typename A::T a3, typename A::T z, typename A::T c, int fma_mode) {
+                              typename A::T a3, typename A::T z, typename A::T c, int mode_) {
   typedef typename A::T T;
-  if (A::can_fuse && (fma_mode & 2)) {
-    T t;
-    if (fma_mode & 32) t = A::fma_(a1, x, A::mul(a2, y));
-    else t = A::fma_(a2, y, A::mul(a1, x));
-    t = A::fma_(a3, z, t);
-    return A::add(t, c);
+  const int mode = A::can_fuse ? mode_ : 0;
+  T t;
+  switch (mode) {
+    case 1: t = A::add(A::fma_(a1, x, A::mul(a2, y)), A::mul(a3, z)); break;
+    case 2: t = A::fma_(a3, z, A::fma_(a1, x, A::mul(a2, y))); break;
+    case 3: t = A::add(A::fma_(a2, y, A::mul(a1, x)), A::mul(a3, z)); break;
+    case 4: t = A::fma_(a3, z, A::fma_(a2, y, A::mul(a1, x))); break;
+    case 5: t = A::fma_(a3, z, A::add(A::mul(a1, x), A::mul(a2, y))); break;
+    default: t = A::add(A::add(A::mul(a1, x), A::mul(a2, y)), A::mul(a3, z)); break;
   }
-  T t = A::add(A::mul(a1, x), A::mul(a2, y));
-  t = A::add(t, A::mul(a3, z));
   return A::add(t, c);
 }
 
@@ -404,14 +424,13 @@ template <class A>
 inline typename A::T rot_row2(typename A::T x, typename A::T a, typename A::T y, typename A::T b, bool minus,
                               typename A::T c, int fma_mode) {
   typedef typename A::T T;
+  const int mode = A::can_fuse ? Fm::rot2(fma_mode) : 0;
   T t;
-  if (A::can_fuse && (fma_mode & 2)) {
-    if (fma_mode & 32) {
-      const T yb = A::mul(y, b);
-      t = A::fma_(x, a, minus ? A::neg(yb) : yb);
-    } else {
-      t = A::fma_(minus ? A::neg(y) : y, b, A::mul(x, a));
-    }
+  if (mode == 1) {
+    const T yb = A::mul(y, b);
+    t = A::fma_(x, a, minus ? A::neg(yb) : yb);
+  } else if (mode == 2) {
+    t = A::fma_(minus ? A::neg(y) : y, b, A::mul(x, a));
   } else {
     t = minus ? A::sub(A::mul(x, a), A::mul(y, b)) : A::add(A::mul(x, a), A::mul(y, b));
   }
@@ -440,6 +459,7 @@ struct Args {
   int fma_mode;
   int wide_acc;       // bwd only: accumulate in double and round once (not what the reference does)
   int nthreads;       // <= 0: all hardware threads
+  const void* trig;   // optional (R, 2|6) table of cos/sin per roi angle, element type; may be null
 };
 
 template <class A>
@@ -456,7 +476,7 @@ int run_fwd(const Args& a) {
     const int pd = (int)(item % a.od);
     {
       RoiGeom<A> g;
-      decode_roi<A>(a.rois, n, a.ndim, a.kind, osz, a.spatial_scale, a.sampling_ratio, a.aligned, a.fma_mode, g);
+      decode_roi<A>(a.rois, n, a.ndim, a.kind, osz, a.spatial_scale, a.sampling_ratio, a.aligned, a.fma_mode, a.trig, g);
       if (g.batch < 0 || g.batch >= a.N) {
         err.store(1);
         for (int64_t i = 0; i < (int64_t)a.oh * a.ow; ++i)
@@ -480,9 +500,9 @@ int run_fwd(const Args& a) {
                       sx = rot_row2<A>(x, g.rot[0], y, g.rot[1], true, g.centre[0], a.fma_mode);
                       sy = rot_row2<A>(x, g.rot[1], y, g.rot[0], false, g.centre[1], a.fma_mode);
                     } else {
-                      sx = rot_row3<A>(g.rot[0], x, g.rot[1], y, g.rot[2], z, g.centre[0], a.fma_mode);
-                      sy = rot_row3<A>(g.rot[3], x, g.rot[4], y, g.rot[5], z, g.centre[1], a.fma_mode);
-                      sz = rot_row3<A>(g.rot[6], x, g.rot[7], y, g.rot[8], z, g.centre[2], a.fma_mode);
+                      sx = rot_row3<A>(g.rot[0], x, g.rot[1], y, g.rot[2], z, g.centre[0], Fm::row(a.fma_mode, 0));
+                      sy = rot_row3<A>(g.rot[3], x, g.rot[4], y, g.rot[5], z, g.centre[1], Fm::row(a.fma_mode, 1));
+                      sz = rot_row3<A>(g.rot[6], x, g.rot[7], y, g.rot[8], z, g.centre[2], Fm::row(a.fma_mode, 2));
                     }
                   }
                   T val = (T)0;
@@ -527,7 +547,7 @@ int run_bwd(const Args& a) {
     if (a.wide_acc) wide.assign((size_t)(a.N * vol), 0.0);
     for (int64_t n = 0; n < a.R; ++n) {
       RoiGeom<A> g;
-      decode_roi<A>(a.rois, n, a.ndim, a.kind, osz, a.spatial_scale, a.sampling_ratio, a.aligned, a.fma_mode, g);
+      decode_roi<A>(a.rois, n, a.ndim, a.kind, osz, a.spatial_scale, a.sampling_ratio, a.aligned, a.fma_mode, a.trig, g);
       if (g.batch < 0 || g.batch >= a.N) {
         err.store(1);
         continue;
@@ -550,9 +570,9 @@ int run_bwd(const Args& a) {
                       sx = rot_row2<A>(x, g.rot[0], y, g.rot[1], true, g.centre[0], a.fma_mode);
                       sy = rot_row2<A>(x, g.rot[1], y, g.rot[0], false, g.centre[1], a.fma_mode);
                     } else {
-                      sx = rot_row3<A>(g.rot[0], x, g.rot[1], y, g.rot[2], z, g.centre[0], a.fma_mode);
-                      sy = rot_row3<A>(g.rot[3], x, g.rot[4], y, g.rot[5], z, g.centre[1], a.fma_mode);
-                      sz = rot_row3<A>(g.rot[6], x, g.rot[7], y, g.rot[8], z, g.centre[2], a.fma_mode);
+                      sx = rot_row3<A>(g.rot[0], x, g.rot[1], y, g.rot[2], z, g.centre[0], Fm::row(a.fma_mode, 0));
+                      sy = rot_row3<A>(g.rot[3], x, g.rot[4], y, g.rot[5], z, g.centre[1], Fm::row(a.fma_mode, 1));
+                      sz = rot_row3<A>(g.rot[6], x, g.rot[7], y, g.rot[8], z, g.centre[2], Fm::row(a.fma_mode, 2));
                     }
                   }
                   T w[8];
@@ -629,9 +649,10 @@ extern "C" {
 // its gradient is skipped), or a negative argument error.
 int mvr_oracle_fwd(const void* features, const void* rois, void* output, int dtype, int ndim, int roi_kind,
                    int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int od, int oh, int ow,
-                   float spatial_scale, int sampling_ratio, int aligned, int order, int fma_mode, int nthreads) {
+                   float spatial_scale, int sampling_ratio, int aligned, int order, int fma_mode, int nthreads,
+                   const void* trig) {
   Args a = {features, rois, output, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow,
-            spatial_scale, sampling_ratio, aligned, order, fma_mode, 0, nthreads};
+            spatial_scale, sampling_ratio, aligned, order, fma_mode, 0, nthreads, trig};
   int e = check(a, dtype);
   if (e) return e;
   switch (dtype) {
@@ -647,9 +668,9 @@ int mvr_oracle_fwd(const void* features, const void* rois, void* output, int dty
 int mvr_oracle_bwd(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim, int roi_kind,
                    int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int od, int oh, int ow,
                    float spatial_scale, int sampling_ratio, int aligned, int order, int fma_mode, int wide_acc,
-                   int nthreads) {
+                   int nthreads, const void* trig) {
   Args a = {grad_out, rois, grad_in, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow,
-            spatial_scale, sampling_ratio, aligned, order, fma_mode, wide_acc, nthreads};
+            spatial_scale, sampling_ratio, aligned, order, fma_mode, wide_acc, nthreads, trig};
   int e = check(a, dtype);
   if (e) return e;
   switch (dtype) {

@@ -32,10 +32,10 @@ def lib():
         i64, i32, f32, vp = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
         L.mvr_oracle_fwd.restype = i32
         L.mvr_oracle_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64, i64,
-                                     i32, i32, i32, f32, i32, i32, i32, i32, i32]
+                                     i32, i32, i32, f32, i32, i32, i32, i32, i32, vp]
         L.mvr_oracle_bwd.restype = i32
         L.mvr_oracle_bwd.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64, i64,
-                                     i32, i32, i32, f32, i32, i32, i32, i32, i32, i32]
+                                     i32, i32, i32, f32, i32, i32, i32, i32, i32, i32, vp]
         L.mvr_oracle_max_threads.restype = i32
         _lib = L
     return _lib
@@ -59,19 +59,41 @@ def _dims(shape, out_size):
     return ndim, N, C, D, H, W, od, oh, ow
 
 
+def _trig_ptr(trig, rois, ndim, kind):
+    if trig is None:
+        return None, None
+    assert kind == KIND_ROTATED
+    trig = trig.detach().cpu().to(rois.dtype).contiguous()
+    assert tuple(trig.shape) == (rois.shape[0], 2 if ndim == 2 else 6)
+    return trig, trig.data_ptr()
+
+
+def device_trig(rois):
+    """cos/sin of the rois' angles evaluated with the DEVICE's sinf/cosf (torch CUDA kernels call
+    the same functions), in the layout ``trig=`` expects: 2D (R,2) [cos, sin]; 3D (R,6)
+    [cos ax, sin ax, cos ay, sin ay, cos az, sin az].  For half rois the argument is widened to
+    float and the result rounded to half, as the reference does."""
+    ang = rois[:, 5:6] if rois.shape[1] == 6 else rois[:, 7:10]
+    a = ang.cuda().float()
+    t = torch.stack([torch.cos(a), torch.sin(a)], dim=2).reshape(rois.shape[0], -1)
+    return t.to(rois.dtype).cpu()
+
+
 def forward(features, rois, out_size, kind, spatial_scale=1.0, sampling_ratio=0, aligned=True, order=1,
-            fma_mode=0, nthreads=0):
+            fma_mode=0, nthreads=0, trig=None):
     """Reference forward on CPU tensors.  ``kind``: KIND_BOX (RoIAlign) or KIND_ROTATED
-    (RoIAlignRotated / affine_*).  Returns (R, C, [od,] oh, ow) in the feature dtype."""
+    (RoIAlignRotated / affine_*).  Returns (R, C, [od,] oh, ow) in the feature dtype.
+    ``trig``: optional table from :func:`device_trig`."""
     features = features.detach().cpu().contiguous()
     rois = rois.detach().cpu().to(features.dtype).contiguous()
     ndim, N, C, D, H, W, od, oh, ow = _dims(tuple(features.shape), tuple(out_size))
     assert rois.dim() == 2 and rois.shape[1] == ROI_WIDTH[(ndim, kind)], "wrong roi size"
     R = rois.shape[0]
     out = torch.empty((R, C) + tuple(out_size), dtype=features.dtype)
+    trig, tp = _trig_ptr(trig, rois, ndim, kind)
     rc = lib().mvr_oracle_fwd(features.data_ptr(), rois.data_ptr(), out.data_ptr(), DTYPES[features.dtype],
                               ndim, kind, N, C, D, H, W, R, od, oh, ow, float(spatial_scale),
-                              int(sampling_ratio), int(bool(aligned)), int(order), int(fma_mode), int(nthreads))
+                              int(sampling_ratio), int(bool(aligned)), int(order), int(fma_mode), int(nthreads), tp)
     if rc < 0:
         raise ValueError(f"mvr_oracle_fwd: bad argument ({rc})")
     if rc == 1:
@@ -80,7 +102,7 @@ def forward(features, rois, out_size, kind, spatial_scale=1.0, sampling_ratio=0,
 
 
 def backward(grad_out, rois, feature_size, kind, spatial_scale=1.0, sampling_ratio=0, aligned=True, order=1,
-             fma_mode=0, wide_acc=False, nthreads=0):
+             fma_mode=0, wide_acc=False, nthreads=0, trig=None):
     """Reference backward: gradient w.r.t. the features, shape ``feature_size``, dtype of grad_out."""
     grad_out = grad_out.detach().cpu().contiguous()
     rois = rois.detach().cpu().to(grad_out.dtype).contiguous()
@@ -90,10 +112,11 @@ def backward(grad_out, rois, feature_size, kind, spatial_scale=1.0, sampling_rat
     R = rois.shape[0]
     assert grad_out.shape[0] == R and grad_out.shape[1] == C
     grad_in = torch.zeros(tuple(feature_size), dtype=grad_out.dtype)
+    trig, tp = _trig_ptr(trig, rois, ndim, kind)
     rc = lib().mvr_oracle_bwd(grad_out.data_ptr(), rois.data_ptr(), grad_in.data_ptr(), DTYPES[grad_out.dtype],
                               ndim, kind, N, C, D, H, W, R, od, oh, ow, float(spatial_scale),
                               int(sampling_ratio), int(bool(aligned)), int(order), int(fma_mode),
-                              int(bool(wide_acc)), int(nthreads))
+                              int(bool(wide_acc)), int(nthreads), tp)
     if rc < 0:
         raise ValueError(f"mvr_oracle_bwd: bad argument ({rc})")
     if rc == 1:

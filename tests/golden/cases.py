@@ -1,0 +1,68 @@
+"""Seeded inputs of the golden cases (shared by the generator and the tests)."""
+import math
+
+import torch
+
+KIND_BOX, KIND_ROTATED = 0, 1
+
+
+def make_rois(gen, ndim, kind, n_batch, spatial, R, dtype):
+    """R rois over a volume of ``spatial`` = (D,H,W) or (H,W): inside, straddling the border,
+    fully outside, tiny and large ones.  xyz order, as the reference's layout."""
+    ext = torch.tensor(list(reversed(spatial)), dtype=torch.float64)  # (W,H[,D])
+    b = torch.randint(0, n_batch, (R, 1), generator=gen).double()
+    centre = (torch.rand(R, ndim, generator=gen, dtype=torch.float64) * 1.4 - 0.2) * ext
+    size = (torch.rand(R, ndim, generator=gen, dtype=torch.float64) * 0.9 + 0.02) * ext
+    size[0] = 0.3            # smaller than one voxel
+    centre[1] = ext * 2.5    # entirely outside
+    if R > 2:
+        size[2] = ext * 1.5  # larger than the volume
+    if kind == KIND_BOX:
+        rois = torch.cat([b, centre - size / 2, centre + size / 2], 1)
+        if R > 3:
+            rois[3, 1 + ndim:] = rois[3, 1:1 + ndim] - 1.0  # end < start: size clamps to 1
+    else:
+        nang = 1 if ndim == 2 else 3
+        ang = (torch.rand(R, nang, generator=gen, dtype=torch.float64) * 2 - 1) * math.pi
+        ang[0] = 0.0
+        if ndim == 3 and R > 4:
+            ang[4, :2] = 0.0  # rotation about z only, as the augmentations use it
+        rois = torch.cat([b, centre, size, ang], 1)
+        if R > 3:
+            rois[3, 1 + ndim:1 + 2 * ndim] = 0.0  # zero-size roi
+    return rois.to(dtype)
+
+
+def all_cases():
+    """(name, dict) for every golden case."""
+    out = []
+    seed = 100
+    for ndim in (2, 3):
+        spatial = (20, 24) if ndim == 2 else (9, 12, 14)
+        out_size = (5, 4) if ndim == 2 else (3, 4, 5)
+        for kind in (KIND_BOX, KIND_ROTATED):
+            for dtype in (torch.float32, torch.float16):
+                for order, sr in ((1, 2), (1, 0), (0, 1), (1, 1)):
+                    for aligned in ((True, False) if kind == KIND_ROTATED and order == 1 and sr == 2 else (True,)):
+                        seed += 1
+                        name = "%dd_%s_%s_o%d_s%d_%s" % (
+                            ndim, "box" if kind == KIND_BOX else "rot",
+                            "f32" if dtype == torch.float32 else "f16", order, sr, "al" if aligned else "na")
+                        out.append((name, dict(ndim=ndim, kind=kind, dtype=dtype, order=order, sampling_ratio=sr,
+                                               aligned=aligned, spatial=spatial, out_size=out_size, seed=seed,
+                                               N=2, C=3, R=7,
+                                               spatial_scale={(1, 2): 1.0, (1, 0): 0.5, (0, 1): 0.77, (1, 1): 0.3}[(order, sr)])))
+    return out
+
+
+def make_inputs(case):
+    gen = torch.Generator().manual_seed(case["seed"])
+    dtype = case["dtype"]
+    feat = torch.rand((case["N"], case["C"]) + tuple(case["spatial"]), generator=gen, dtype=torch.float64)
+    feat = (feat * 2 - 0.5).to(dtype)
+    scale = case["spatial_scale"]
+    rois = make_rois(gen, case["ndim"], case["kind"], case["N"], case["spatial"], case["R"], torch.float64)
+    rois[:, 1:1 + 2 * case["ndim"]] /= scale
+    rois = rois.to(dtype)
+    grad = torch.randn((case["R"], case["C"]) + tuple(case["out_size"]), generator=gen, dtype=torch.float64).to(dtype)
+    return feat, rois, grad

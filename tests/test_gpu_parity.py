@@ -1,0 +1,261 @@
+"""GPU parity: the CUDA library, called through its C ABI (medvision_b200._C -> libmvr.so),
+against (a) the committed outputs of the reference's own kernels, (b) the CPU restatement on the
+same seeded inputs, (c) the reference's kernels run live when oracle/_ref is present, and
+(d) size-independent properties at the benchmark's full sizes."""
+import math
+
+import pytest
+import torch
+
+import cases
+from oracle import port, ref
+from util import BWD_TOL, FWD_TOL, assert_close, golden_tensor, load_golden, n_mismatch
+
+pytestmark = pytest.mark.gpu
+
+REF_FM = 1 | (1 << 1) | (1 << 2) | (1 << 3) | (1 << 5) | (1 << 7) | (1 << 10) | (1 << 13) | \
+    (1 << 16) | (1 << 18) | (2 << 20) | (1 << 22)
+CASES = cases.all_cases()
+GOLD = load_golden()
+
+
+def _kw(c):
+    return dict(spatial_scale=c["spatial_scale"], sampling_ratio=c["sampling_ratio"],
+                aligned=c["aligned"], order=c["order"])
+
+
+def lib_forward(f, r, out_size, kind, spatial_scale=1.0, sampling_ratio=0, aligned=True, order=1, affine=False):
+    from medvision_b200 import _C
+    nd = f.dim() - 2
+    out = torch.full((r.size(0), f.size(1)) + tuple(out_size), float("nan"), dtype=f.dtype, device=f.device)
+    if kind == cases.KIND_BOX:
+        fn = _C.roi_align_2d_forward if nd == 2 else _C.roi_align_3d_forward
+        fn(f, r, out, *out_size, spatial_scale, sampling_ratio, order)
+    elif affine:
+        fn = _C.affine_2d if nd == 2 else _C.affine_3d
+        fn(f, r, out, *out_size, spatial_scale, sampling_ratio, aligned, order)
+    else:
+        fn = _C.roi_align_rotated_2d_forward if nd == 2 else _C.roi_align_rotated_3d_forward
+        fn(f, r, out, *out_size, spatial_scale, sampling_ratio, aligned, order)
+    return out
+
+
+def lib_backward(g, r, fshape, kind, spatial_scale=1.0, sampling_ratio=0, aligned=True, order=1):
+    from medvision_b200 import _C
+    nd = len(fshape) - 2
+    gin = torch.zeros(tuple(fshape), dtype=g.dtype, device=g.device)
+    out_size = tuple(g.shape[2:])
+    if kind == cases.KIND_BOX:
+        fn = _C.roi_align_2d_backward if nd == 2 else _C.roi_align_3d_backward
+        fn(g, r, gin, *out_size, spatial_scale, sampling_ratio, order)
+    else:
+        fn = _C.roi_align_rotated_2d_backward if nd == 2 else _C.roi_align_rotated_3d_backward
+        fn(g, r, gin, *out_size, spatial_scale, sampling_ratio, aligned, order)
+    return gin
+
+
+# ------------------------------------------------------------------ golden cases (general kernels)
+@pytest.mark.parametrize("name,case", CASES, ids=[n for n, _ in CASES])
+def test_forward_golden_bit_exact(name, case):
+    feat, rois, _ = cases.make_inputs(case)
+    out = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], **_kw(case))
+    gold = golden_tensor(GOLD, name + "/fwd", case["dtype"])
+    # same rounding sequence, same device sinf/cosf: identical bits to the reference's kernels
+    assert n_mismatch(out, gold) == 0
+    # the restatement with the device's sin/cos values: bit-exact in float as well
+    trig = port.device_trig(rois) if case["kind"] == cases.KIND_ROTATED else None
+    oracle = port.forward(feat, rois, case["out_size"], case["kind"], trig=trig,
+                          fma_mode=REF_FM if case["dtype"] == torch.float32 else 0, **_kw(case))
+    assert n_mismatch(out, oracle) == 0
+
+
+@pytest.mark.parametrize("name,case", CASES, ids=[n for n, _ in CASES])
+def test_backward_golden(name, case):
+    feat, rois, grad = cases.make_inputs(case)
+    gin = lib_backward(grad.cuda(), rois.cuda(), feat.shape, case["kind"], **_kw(case))
+    gold = golden_tensor(GOLD, name + "/bwd", case["dtype"])
+    assert_close(gin, gold, BWD_TOL[case["dtype"]], name + " vs reference kernels")
+    oracle = port.backward(grad, rois, feat.shape, case["kind"],
+                           fma_mode=REF_FM if case["dtype"] == torch.float32 else 0, **_kw(case))
+    assert_close(gin, oracle, BWD_TOL[case["dtype"]], name + " vs restatement")
+
+
+@pytest.mark.parametrize("name,case", [(n, c) for n, c in CASES if c["kind"] == cases.KIND_ROTATED and c["order"] == 1],
+                         ids=[n for n, c in CASES if c["kind"] == cases.KIND_ROTATED and c["order"] == 1])
+def test_affine_entry_equals_rotated_entry(name, case):
+    feat, rois, _ = cases.make_inputs(case)
+    a = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], affine=True, **_kw(case))
+    b = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], **_kw(case))
+    assert n_mismatch(a, b) == 0
+
+
+# ------------------------------------------------------------------ streaming 3D kernel
+def dense_case(kind, dtype, rot, order, out_size, spatial, seed, R=5, C=2, N=2, scale=1.0):
+    """Dense resampling rois (one sample per voxel) like the augmentations build them."""
+    g = torch.Generator().manual_seed(seed)
+    D, H, W = spatial
+    feat = (torch.rand((N, C, D, H, W), generator=g, dtype=torch.float64) * 2 - 0.5).to(dtype)
+    ext = torch.tensor([W, H, D], dtype=torch.float64)
+    b = torch.randint(0, N, (R, 1), generator=g).double()
+    centre = ext / 2 + (torch.rand(R, 3, generator=g, dtype=torch.float64) - 0.5) * ext * 0.5
+    size = ext * (0.5 + torch.rand(R, 3, generator=g, dtype=torch.float64))
+    if kind == cases.KIND_BOX:
+        rois = torch.cat([b, (centre - size / 2) / scale, (centre + size / 2) / scale], 1)
+    else:
+        ang = (torch.rand(R, 3, generator=g, dtype=torch.float64) * 2 - 1) * math.pi / 5
+        if rot == "none":
+            ang[:] = 0
+        elif rot == "z":
+            ang[:, :2] = 0
+        rois = torch.cat([b, centre / scale, size / scale, ang], 1)
+        rois[0, 7:] = 0  # always one unrotated roi
+    return feat, rois.to(dtype)
+
+
+STREAM = []
+for dtype in (torch.float16, torch.float32):
+    for kind, rot in ((cases.KIND_ROTATED, "none"), (cases.KIND_ROTATED, "z"), (cases.KIND_ROTATED, "xyz"),
+                      (cases.KIND_BOX, "none")):
+        for order in (1, 0):
+            STREAM.append((dtype, kind, rot, order, (17, 18, 40), (12, 20, 33), 1.0))
+    # odd output width (scalar stores), tiles that do not divide, more depth than one chunk
+    STREAM.append((dtype, cases.KIND_ROTATED, "z", 1, (70, 19, 35), (30, 17, 41), 0.77))
+    STREAM.append((dtype, cases.KIND_ROTATED, "xyz", 1, (9, 33, 34), (8, 9, 10), 1.0))
+
+
+@pytest.mark.parametrize("dtype,kind,rot,order,out_size,spatial,scale", STREAM,
+                         ids=["%s-%s-%s-o%d-%s" % (str(s[0])[6:], "rot" if s[1] else "box", s[2], s[3],
+                                                   "x".join(map(str, s[4]))) for s in STREAM])
+def test_streaming_kernel_matches_restatement_and_reference(dtype, kind, rot, order, out_size, spatial, scale):
+    feat, rois = dense_case(kind, dtype, rot, order, out_size, spatial, seed=11 + order + len(rot), scale=scale)
+    kw = dict(spatial_scale=scale, sampling_ratio=1, aligned=True, order=order)
+    out = lib_forward(feat.cuda(), rois.cuda(), out_size, kind, **kw)
+    assert not torch.isnan(out).any(), "every output element must be written"
+    trig = port.device_trig(rois) if kind == cases.KIND_ROTATED else None
+    oracle = port.forward(feat, rois, out_size, kind, trig=trig,
+                          fma_mode=REF_FM if dtype == torch.float32 else 0, **kw)
+    assert n_mismatch(out, oracle) == 0, "bit-exact against the CPU restatement"
+    if ref.available():
+        r = ref.forward(feat.cuda(), rois.cuda(), out_size, kind, **kw)
+        assert n_mismatch(out, r) == 0, "bit-exact against the reference's own kernel"
+
+
+def test_streaming_kernel_unaligned_output_pointer():
+    feat, rois = dense_case(cases.KIND_ROTATED, torch.float16, "z", 1, (16, 16, 32), (10, 12, 14), seed=5)
+    kw = dict(spatial_scale=1.0, sampling_ratio=1, aligned=True, order=1)
+    from medvision_b200 import _C
+    R, C = rois.size(0), feat.size(1)
+    n = R * C * 16 * 16 * 32
+    buf = torch.zeros(n + 1, dtype=torch.float16, device="cuda")
+    out = buf[1:].view(R, C, 16, 16, 32)  # 2-byte aligned only
+    _C.affine_3d(feat.cuda(), rois.cuda(), out, 16, 16, 32, 1.0, 1, True, 1)
+    oracle = port.forward(feat, rois, (16, 16, 32), cases.KIND_ROTATED, **kw)
+    assert n_mismatch(out, oracle) == 0
+
+
+# ------------------------------------------------------------------ behaviour at the boundary
+def test_bad_batch_index_sets_status_and_writes_zeros():
+    from medvision_b200 import _C
+    _C.last_status()
+    feat = torch.rand(1, 1, 8, 8, device="cuda")
+    rois = torch.tensor([[0, 1, 1, 5, 5], [2, 1, 1, 5, 5]], dtype=torch.float32, device="cuda")
+    out = lib_forward(feat, rois, (3, 3), cases.KIND_BOX, 1.0, 2, True, 1)
+    assert torch.count_nonzero(out[1]) == 0 and torch.count_nonzero(out[0]) > 0
+    assert _C.last_status() & 1
+    assert _C.last_status() == 0
+
+
+def test_empty_roi_list_is_a_noop():
+    feat = torch.rand(1, 2, 8, 8, device="cuda")
+    out = lib_forward(feat, torch.zeros(0, 5, device="cuda"), (3, 3), cases.KIND_BOX)
+    assert out.shape == (0, 2, 3, 3)
+
+
+def test_wrong_roi_width_and_dtype_raise():
+    from medvision_b200 import _C
+    feat = torch.rand(1, 1, 4, 4, 4, device="cuda")
+    out = torch.empty(1, 1, 2, 2, 2, device="cuda")
+    with pytest.raises(RuntimeError, match="wrong roi size! size_rois should be 10"):
+        _C.affine_3d(feat, torch.zeros(1, 7, device="cuda"), out, 2, 2, 2, 1.0, 1, True, 1)
+    with pytest.raises(RuntimeError, match="expected scalar type"):
+        _C.roi_align_rotated_3d_forward(feat, torch.zeros(1, 10, device="cuda", dtype=torch.float16), out,
+                                        2, 2, 2, 1.0, 1, True, 1)
+
+
+def test_non_contiguous_features_are_copied_like_the_reference():
+    feat = torch.rand(2, 3, 10, 12, device="cuda").transpose(2, 3)  # (2,3,12,10) non-contiguous
+    rois = torch.tensor([[1, 1.5, 2.0, 8.0, 9.5]], device="cuda")
+    a = lib_forward(feat, rois, (4, 4), cases.KIND_BOX, 1.0, 2, True, 1)
+    b = lib_forward(feat.contiguous(), rois, (4, 4), cases.KIND_BOX, 1.0, 2, True, 1)
+    assert torch.equal(a, b)
+
+
+def test_module_and_autograd_against_restatement():
+    from medvision_b200.ops import RoIAlign, RoIAlignRotated
+    case = [c for n, c in CASES if n == "3d_rot_f32_o1_s2_al"][0]
+    feat, rois, grad = cases.make_inputs(case)
+    f = feat.cuda().requires_grad_(True)
+    m = RoIAlignRotated(case["out_size"], 1.0, sampling_ratio=2, aligned=True)
+    out = m(f, rois.cuda())
+    out.backward(grad.cuda())
+    assert_close(f.grad, port.backward(grad, rois, feat.shape, cases.KIND_ROTATED, fma_mode=REF_FM, **_kw(case)),
+                 BWD_TOL[torch.float32], "autograd")
+    # order 0 forces one sample per bin
+    case0 = [c for n, c in CASES if n == "2d_box_f32_o0_s1_al"][0]
+    feat, rois, _ = cases.make_inputs(case0)
+    out0 = RoIAlign(case0["out_size"], case0["spatial_scale"], sampling_ratio=4)(feat.cuda(), rois.cuda(), order=0)
+    assert n_mismatch(out0, golden_tensor(GOLD, "2d_box_f32_o0_s1_al/fwd", torch.float32)) == 0
+
+
+def test_double_precision_and_adjointness():
+    case = dict(ndim=3, kind=cases.KIND_ROTATED, dtype=torch.float64, order=1, sampling_ratio=2, aligned=True,
+                spatial=(6, 7, 9), out_size=(3, 4, 5), seed=9, N=2, C=2, R=6, spatial_scale=0.5)
+    feat, rois, grad = cases.make_inputs(case)
+    out = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], **_kw(case))
+    gin = lib_backward(grad.cuda(), rois.cuda(), feat.shape, case["kind"], **_kw(case))
+    assert_close(out, port.forward(feat, rois, case["out_size"], case["kind"], fma_mode=REF_FM, **_kw(case)), 1e-12)
+    lhs = float((out.cpu() * grad).sum())
+    rhs = float((feat * gin.cpu()).sum())
+    assert abs(lhs - rhs) <= 1e-10 * max(1.0, abs(lhs))
+
+
+# ------------------------------------------------------------------ full-size properties
+def ct_like(shape, seed, device="cuda"):
+    g = torch.Generator(device=device).manual_seed(seed)
+    v = torch.empty(shape, device=device).normal_(-300, 400, generator=g).round_().clamp_(-1024, 3071)
+    return ((v + 1024) / 4095).half()
+
+
+def test_full_size_identity_resample_is_exact():
+    """Whole-volume roi, output size = volume size: every sample falls on a voxel centre, so the
+    resampled volume equals the input bit for bit (half coordinates up to 512 are exact)."""
+    from medvision_b200.ops import affine_3d
+    vol = ct_like((2, 1, 160, 512, 512), 3)
+    rois = torch.tensor([[i, 256, 256, 80, 512, 512, 160, 0, 0, 0] for i in range(2)], dtype=torch.float16)
+    out = affine_3d(vol, rois.cuda(), (160, 512, 512), 1.0, 1, True, 1)
+    assert torch.equal(out, vol)
+    out0 = affine_3d(vol, rois.cuda(), (160, 512, 512), 1.0, 1, True, 0)
+    assert torch.equal(out0, vol)
+
+
+def test_full_size_resize_slab_against_restatement():
+    """Config 'Batched 3D Resize' (160,512,512) -> (128,256,256): full-size launch on the GPU,
+    a slab of it checked against the CPU restatement, the rest through linearity."""
+    from medvision_b200.ops import affine_3d
+    vol = ct_like((1, 1, 160, 512, 512), 4)
+    rois = torch.tensor([[0, 256, 256, 80, 512, 512, 160, 0, 0, 0]], dtype=torch.float16)
+    out = affine_3d(vol, rois.cuda(), (128, 256, 256), 1.0, 1, True, 1)
+    assert float(out.min()) >= 0.0 and float(out.max()) <= 1.0  # convex combinations of [0,1] data
+    # The same output slab from a sub-volume call on the CPU: depth rows 40..47 of the output
+    # come from input planes 50..60 only; a roi on the cropped volume shifted by 50 planes
+    # produces different roundings, so instead compare the restatement on the full problem
+    # restricted by running it on a 16-plane-deep output (same roi, od=128 needed for bins):
+    oracle = port.forward(vol.cpu()[:, :, :, :64, :64].contiguous(),
+                          torch.tensor([[0, 32, 32, 80, 64, 64, 160, 0, 0, 0]], dtype=torch.float16),
+                          (128, 32, 32), cases.KIND_ROTATED, 1.0, 1, True, 1)
+    small = affine_3d(vol[:, :, :, :64, :64].contiguous(),
+                      torch.tensor([[0, 32, 32, 80, 64, 64, 160, 0, 0, 0]], dtype=torch.float16).cuda(),
+                      (128, 32, 32), 1.0, 1, True, 1)
+    assert n_mismatch(small, oracle) == 0
+    # interior of the big result equals the small one where both read the same voxels
+    assert n_mismatch(out[0, 0, :, :31, :31], small[0, 0, :, :31, :31]) == 0
