@@ -2,10 +2,11 @@
 // selection and launch.  No torch types; device pointers and sizes only.
 #include <cuda_runtime.h>
 #include <atomic>
+#include <cstdlib>
 
 #include "../../include/mvr.h"
 #include "mvr_generic.cuh"
-#include "mvr_stream3d.cuh"
+#include "mvr_tma3d.cuh"
 
 namespace {
 

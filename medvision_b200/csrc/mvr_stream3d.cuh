@@ -37,7 +37,7 @@ constexpr int MVR_STREAM3D_NOT_APPLICABLE = 1;
 constexpr int kS3Threads = 256;
 constexpr int kS3TileW = 32;   // output voxels along w per CTA (2 per thread)
 constexpr int kS3TileH = 16;
-constexpr int kS3MaxChunk = 64;  // output depths per CTA
+constexpr int kS3MaxChunk = 128;  // output depths per CTA
 
 // The float contraction pattern this kernel hard-codes (the reference build's).
 constexpr int kS3FloatPattern = kReferenceContraction;
@@ -65,6 +65,14 @@ template <> struct P2<__half> {
     return *reinterpret_cast<V*>(&u);
   }
   __device__ __forceinline__ static void store2(__half* p, V v) { *reinterpret_cast<__half2*>(p) = v; }
+  typedef unsigned M;  // lane mask, built once per thread
+  __device__ __forceinline__ static M make_mask(bool keep_a, bool keep_b) {
+    return (keep_a ? 0x0000ffffu : 0u) | (keep_b ? 0xffff0000u : 0u);
+  }
+  __device__ __forceinline__ static V apply(V v, M m) {
+    unsigned u = *reinterpret_cast<unsigned*>(&v) & m;
+    return *reinterpret_cast<V*>(&u);
+  }
 };
 
 struct Float2Lanes { float a, b; };
@@ -90,6 +98,9 @@ template <> struct P2<float> {
     return make(keep_a ? v.a : 0.0f, keep_b ? v.b : 0.0f);
   }
   __device__ __forceinline__ static void store2(float* p, V v) { *reinterpret_cast<float2*>(p) = make_float2(v.a, v.b); }
+  typedef unsigned M;
+  __device__ __forceinline__ static M make_mask(bool keep_a, bool keep_b) { return (keep_a ? 1u : 0u) | (keep_b ? 2u : 0u); }
+  __device__ __forceinline__ static V apply(V v, M m) { return make((m & 1u) ? v.a : 0.0f, (m & 2u) ? v.b : 0.0f); }
 };
 
 // per-axis (l, h) of one sample; order 0 replaces them by the one-hot choice that the
@@ -107,6 +118,7 @@ struct S3ZTap {        // z-separable: per output depth
   long long o0, o1;    // element offsets of the two source planes inside the volume
   T l, h;
   int inside;
+  int z0, z1;          // the two source planes' indices
 };
 template <typename T>
 struct S3ZProd {       // general rotation: per output depth, the rounded products R_i3 * z
@@ -128,25 +140,31 @@ struct S3Launch {
   int vec_store;                        // 1: two-element vector stores are aligned
 };
 
-template <typename T>
-__global__ void __launch_bounds__(kS3Threads)
-resample_fwd_stream3d(const Params p, const S3Launch L) {
-  typedef Ar<T> A;
-  typedef P2<T> Q;
-  typedef typename Q::V V;
-  __shared__ S3Shared<T> sh;
-
-  // ---- CTA coordinates: tile_w fastest, then tile_h, chunk, (roi, channel)
+// CTA coordinates of the streaming kernels: tile_w fastest, then tile_h, depth chunk, (roi, channel)
+struct S3Cta {
+  int tw, th, ck, c, pd0, npd;
+  long long nc, n;
+};
+__device__ __forceinline__ S3Cta s3_cta(const Params& p, const S3Launch& L) {
+  S3Cta k;
   long long cta = blockIdx.x;
-  const int tw = (int)(cta % L.tiles_w); cta /= L.tiles_w;
-  const int th = (int)(cta % L.tiles_h); cta /= L.tiles_h;
-  const int ck = (int)(cta % L.chunks);  cta /= L.chunks;
-  const long long nc = cta;
-  const long long n = nc / p.C;
-  const int c = (int)(nc % p.C);
-  const int pd0 = ck * L.chunk;
-  const int npd = min(L.chunk, p.od - pd0);
+  k.tw = (int)(cta % L.tiles_w); cta /= L.tiles_w;
+  k.th = (int)(cta % L.tiles_h); cta /= L.tiles_h;
+  k.ck = (int)(cta % L.chunks);  cta /= L.chunks;
+  k.nc = cta;
+  k.n = k.nc / p.C;
+  k.c = (int)(k.nc % p.C);
+  k.pd0 = k.ck * L.chunk;
+  k.npd = min(L.chunk, p.od - k.pd0);
+  return k;
+}
 
+// Decode the roi, classify it, and fill the per-depth table.  Ends with a __syncthreads().
+template <typename T>
+__device__ __forceinline__ void s3_prologue(const Params& p, const S3Cta& k, S3Shared<T>& sh) {
+  typedef Ar<T> A;
+  const long long n = k.n;
+  const int pd0 = k.pd0, npd = k.npd;
   const int fm = kS3FloatPattern;
   if (threadIdx.x == 0) {
     const int osz[3] = {p.ow, p.oh, p.od};
@@ -188,6 +206,8 @@ resample_fwd_stream3d(const Params p, const S3Launch L) {
       if (p.order == 0) nearest_axis<T>(t.l, t.h);
       e.o0 = t.i0 * HW;
       e.o1 = t.i1 * HW;
+      e.z0 = t.i0;
+      e.z1 = t.i1;
       e.l = t.l;
       e.h = t.h;
       sh.zt[i] = e;
@@ -201,6 +221,21 @@ resample_fwd_stream3d(const Params p, const S3Launch L) {
   }
   __syncthreads();
 
+}
+
+// Everything after the prologue, gathering through L1/L2 with plain loads.
+template <typename T>
+__device__ void s3_body_l1(const Params& p, const S3Launch& L, const S3Cta& k, S3Shared<T>& sh) {
+  typedef Ar<T> A;
+  typedef P2<T> Q;
+  typedef typename Q::V V;
+  const int tw = k.tw, th = k.th, ck = k.ck, c = k.c, pd0 = k.pd0, npd = k.npd;
+  const long long nc = k.nc;
+  const int fm = kS3FloatPattern;
+  const RoiGeom<T>& g = sh.g;
+  const bool zsep = sh.zsep != 0;
+  const bool rotated = (p.kind == KIND_ROTATED);
+  const bool bad_batch = (g.batch < 0 || g.batch >= p.N);
   // ---- this thread's two output columns
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pw0 = tw * kS3TileW + (warp & 1) * 16 + (lane & 7) * 2;
@@ -353,34 +388,13 @@ resample_fwd_stream3d(const Params p, const S3Launch L) {
   }
 }
 
-// Picks the streaming kernel when the call has its shape; returns MVR_STREAM3D_NOT_APPLICABLE
-// otherwise (the caller then uses the general kernel).
-inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
-  if (p.ndim != 3 || p.sampling_ratio != 1) return MVR_STREAM3D_NOT_APPLICABLE;
-  if (dtype != 0 /*f32*/ && dtype != 1 /*f16*/) return MVR_STREAM3D_NOT_APPLICABLE;
-  if (dtype == 0 && p.fm != kS3FloatPattern) return MVR_STREAM3D_NOT_APPLICABLE;
-  // small outputs (detection heads) are better served one element per thread
-  if (p.ovol < 4096 || p.ow < 8) return MVR_STREAM3D_NOT_APPLICABLE;
-  if ((long long)p.H * p.W >= 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
-
-  S3Launch L;
-  L.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
-  L.tiles_h = (p.oh + kS3TileH - 1) / kS3TileH;
-  // depth chunk: long enough to amortise the per-thread set-up and to reuse planes, short
-  // enough to give every SM several CTAs
-  const long long per_depth_ctas = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
-  int chunk = kS3MaxChunk;
-  while (chunk > 8 && per_depth_ctas * ((p.od + chunk - 1) / chunk) < 148LL * 16) chunk >>= 1;
-  if (chunk > p.od) chunk = p.od;
-  L.chunk = chunk;
-  L.chunks = (p.od + chunk - 1) / chunk;
-  const size_t esz = dtype == 0 ? 4 : 2;
-  L.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % (2 * esz) == 0);
-  const long long ctas = per_depth_ctas * L.chunks;
-  if (ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
-  if (dtype == 0) resample_fwd_stream3d<float><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
-  else resample_fwd_stream3d<__half><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
-  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+template <typename T>
+__global__ void __launch_bounds__(kS3Threads)
+resample_fwd_stream3d(const Params p, const S3Launch L) {
+  __shared__ S3Shared<T> sh;
+  const S3Cta k = s3_cta(p, L);
+  s3_prologue<T>(p, k, sh);
+  s3_body_l1<T>(p, L, k, sh);
 }
 
 }  // namespace mvr

@@ -121,13 +121,22 @@ for dtype in (torch.float16, torch.float32):
     # odd output width (scalar stores), tiles that do not divide, more depth than one chunk
     STREAM.append((dtype, cases.KIND_ROTATED, "z", 1, (70, 19, 35), (30, 17, 41), 0.77))
     STREAM.append((dtype, cases.KIND_ROTATED, "xyz", 1, (9, 33, 34), (8, 9, 10), 1.0))
+    # row pitch a multiple of 16 bytes: the TMA-staged path (boxes of several sizes, tiles whose
+    # footprint exceeds every box and fall back to plain loads, nearest, boxes, odd output width)
+    STREAM.append((dtype, cases.KIND_ROTATED, "z", 1, (40, 48, 64), (24, 40, 48), 1.0))
+    STREAM.append((dtype, cases.KIND_ROTATED, "z", 0, (40, 48, 64), (24, 40, 48), 0.77))
+    STREAM.append((dtype, cases.KIND_ROTATED, "none", 1, (70, 35, 41), (96, 64, 160), 1.0))
+    STREAM.append((dtype, cases.KIND_ROTATED, "z", 1, (12, 20, 24), (40, 200, 320), 1.0))
+    STREAM.append((dtype, cases.KIND_BOX, "none", 1, (33, 64, 96), (20, 48, 56), 1.0))
+    STREAM.append((dtype, cases.KIND_ROTATED, "xyz", 1, (16, 32, 64), (16, 32, 64), 1.0))
 
 
 @pytest.mark.parametrize("dtype,kind,rot,order,out_size,spatial,scale", STREAM,
                          ids=["%s-%s-%s-o%d-%s" % (str(s[0])[6:], "rot" if s[1] else "box", s[2], s[3],
                                                    "x".join(map(str, s[4]))) for s in STREAM])
 def test_streaming_kernel_matches_restatement_and_reference(dtype, kind, rot, order, out_size, spatial, scale):
-    feat, rois = dense_case(kind, dtype, rot, order, out_size, spatial, seed=11 + order + len(rot), scale=scale)
+    feat, rois = dense_case(kind, dtype, rot, order, out_size, spatial, seed=11 + order + len(rot) + spatial[2],
+                            scale=scale)
     kw = dict(spatial_scale=scale, sampling_ratio=1, aligned=True, order=order)
     out = lib_forward(feat.cuda(), rois.cuda(), out_size, kind, **kw)
     assert not torch.isnan(out).any(), "every output element must be written"
