@@ -59,7 +59,7 @@ def crop_rois(n_vol, per_vol, vol_shape, seed):
 
 
 def workload_c5(device, rank, small=False):
-    n_vol, per_vol = (2, 16) if small else (8, 64)
+    n_vol, per_vol = (2, 64) if small else (8, 64)
     shape = (1, 256, 512, 512)
     vol = ct_like((n_vol,) + shape, 5 + rank, device)
     rois = crop_rois(n_vol, per_vol, shape[1:], 5 + rank)

@@ -138,6 +138,7 @@ struct S3Shared {
 struct S3Launch {
   int tiles_w, tiles_h, chunks, chunk;  // chunk = output depths per CTA
   int vec_store;                        // 1: two-element vector stores are aligned
+  int ring_bytes;                       // TMA-staged kernel: bytes of the shared-memory plane ring
 };
 
 // CTA coordinates of the streaming kernels: tile_w fastest, then tile_h, depth chunk, (roi, channel)

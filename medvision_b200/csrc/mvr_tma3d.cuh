@@ -32,13 +32,13 @@ namespace mvr {
 
 enum { STATUS_TMA_TIMEOUT = 2 };
 
-constexpr int kT3RingBytes = 40960;   // shared-memory ring of plane boxes
-constexpr int kT3MaxStages = 12;
+constexpr int kT3MaxStages = 16;      // ring slots (the ring itself is sized at launch)
 constexpr int kT3MaxBoxBytes = 12800; // largest box; leaves three ring slots
 constexpr int kT3MaxBoxes = 6;
 constexpr int kT3MaxPlanes = 2 * kS3MaxChunk;
 constexpr unsigned kT3SpinLimit = 1u << 22;
 constexpr int kT3Threads = kS3Threads + 32;  // 8 consumer warps + 1 producer warp
+constexpr int kT3Pairs = 2;                   // voxel pairs per consumer thread
 
 struct T3Maps {
   CUtensorMap map[kT3MaxBoxes];  // same tensor (W, H, N*C*D), different box sizes, ascending
@@ -51,9 +51,9 @@ template <typename T>
 struct __align__(8) T3Ent {
   T h, l;               // z weights
   unsigned short adv;   // new planes to take from the ring before this depth (0, 1 or 2)
-  unsigned short flags; // T3_INSIDE, T3_SAME
+  unsigned short flags; // T3_INSIDE
 };
-enum { T3_INSIDE = 1, T3_SAME = 2 };  // SAME: both z taps are the newest plane
+enum { T3_INSIDE = 1 };
 
 template <typename T>
 struct T3Shared {
@@ -63,8 +63,6 @@ struct T3Shared {
   int plane[kT3MaxPlanes];                 // plane schedule: source plane index, in order of use
   T3Ent<T> ent[kS3MaxChunk];
   int warp_tot[4];
-  int starts;                              // depths that start a run of inside depths (must be <= 1)
-  int ok;                                  // 0: the plane order is not of the expected form -> plain loads
   int box[4];                              // xmin, xmax, ymin, ymax over the tile's inside voxels
   volatile int abort_flag;
 };
@@ -74,13 +72,13 @@ __device__ __forceinline__ unsigned t3_smem(const void* p) { return (unsigned)__
 __device__ __forceinline__ void t3_mbar_init(unsigned long long* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(t3_smem(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ void t3_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(t3_smem(bar)), "r"(bytes) : "memory");
+__device__ __forceinline__ void t3_mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void t3_mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(t3_smem(bar)) : "memory");
+__device__ __forceinline__ void t3_mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool t3_mbar_try_wait(unsigned long long* bar, unsigned parity) {
+__device__ __forceinline__ bool t3_mbar_try_wait(unsigned bar, unsigned parity) {
   unsigned ok;
   asm volatile(
       "{\n"
@@ -89,12 +87,12 @@ __device__ __forceinline__ bool t3_mbar_try_wait(unsigned long long* bar, unsign
       "  selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(t3_smem(bar)), "r"(parity)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
 // Bounded wait: false when the limit is reached or another thread of the CTA gave up.
-__device__ __forceinline__ bool t3_mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool t3_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
   if (t3_mbar_try_wait(bar, parity)) return true;
   for (unsigned spin = 0; spin < kT3SpinLimit; ++spin) {
     if (t3_mbar_try_wait(bar, parity)) return true;
@@ -103,71 +101,97 @@ __device__ __forceinline__ bool t3_mbar_wait(unsigned long long* bar, unsigned p
   }
   return false;
 }
-__device__ __forceinline__ void t3_tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned long long* bar, int x,
-                                               int y, int z) {
+__device__ __forceinline__ void t3_tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y,
+                                               int z) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(t3_smem(bar))
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
 
-// the four in-plane taps of this thread's two voxels, out of one ring slot
+// Two elements from two 32-bit shared-memory addresses, as the two lanes of a pair.
 template <typename T>
-__device__ __forceinline__ void t3_read_plane(const unsigned char* sa, const unsigned char* sb, unsigned row,
-                                              typename P2<T>::V* q) {
-  typedef P2<T> Q;
-  const T* a0 = reinterpret_cast<const T*>(sa);
-  const T* b0 = reinterpret_cast<const T*>(sb);
-  const T* a1 = reinterpret_cast<const T*>(sa + row);
-  const T* b1 = reinterpret_cast<const T*>(sb + row);
-  q[0] = Q::make(a0[0], b0[0]);
-  q[1] = Q::make(a0[1], b0[1]);
-  q[2] = Q::make(a1[0], b1[0]);
-  q[3] = Q::make(a1[1], b1[1]);
+__device__ __forceinline__ typename P2<T>::V t3_lds_pair(unsigned addr_a, unsigned addr_b);
+template <>
+__device__ __forceinline__ __half2 t3_lds_pair<__half>(unsigned addr_a, unsigned addr_b) {
+  unsigned va, vb;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(va) : "r"(addr_a) : "memory");
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(vb) : "r"(addr_b) : "memory");
+  const unsigned packed = __byte_perm(va, vb, 0x5410);
+  return *reinterpret_cast<const __half2*>(&packed);
+}
+template <>
+__device__ __forceinline__ Float2Lanes t3_lds_pair<float>(unsigned addr_a, unsigned addr_b) {
+  Float2Lanes v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v.a) : "r"(addr_a) : "memory");
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v.b) : "r"(addr_b) : "memory");
+  return v;
 }
 
-// the reference's tap sum for two voxels at once: older plane first (w1..w4), newer plane last
-template <typename T>
-__device__ __forceinline__ typename P2<T>::V t3_interp(T h, T l, typename P2<T>::V hy2, typename P2<T>::V ly2,
-                                                       typename P2<T>::V hx2, typename P2<T>::V lx2,
-                                                       const typename P2<T>::V* p0, const typename P2<T>::V* p1) {
-  typedef P2<T> Q;
-  typedef typename Q::V V;
-  const V hz2 = Q::dup(h), lz2 = Q::dup(l);
-  const V hzhy = Q::mul(hz2, hy2), hzly = Q::mul(hz2, ly2);
-  const V lzhy = Q::mul(lz2, hy2), lzly = Q::mul(lz2, ly2);
-  V acc = Q::tap_first(Q::mul(hzhy, hx2), p0[0], Q::mul(hzhy, lx2), p0[1]);
-  acc = Q::tap_next(acc, Q::mul(hzly, hx2), p0[2]);
-  acc = Q::tap_next(acc, Q::mul(hzly, lx2), p0[3]);
-  acc = Q::tap_next(acc, Q::mul(lzhy, hx2), p1[0]);
-  acc = Q::tap_next(acc, Q::mul(lzhy, lx2), p1[1]);
-  acc = Q::tap_next(acc, Q::mul(lzly, hx2), p1[2]);
-  acc = Q::tap_next(acc, Q::mul(lzly, lx2), p1[3]);
-  return acc;
+// Bounded wait written as one PTX loop (no divergence bookkeeping around it): up to
+// kT3WaitTries tries, each of which may suspend the thread for up to the time hint.
+constexpr unsigned kT3WaitTries = 1u << 16;
+__device__ __forceinline__ bool t3_mbar_wait_ptx(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n"
+      "  .reg .pred p, q;\n"
+      "  .reg .u32 c;\n"
+      "  mov.u32 c, 0;\n"
+      "T3_WAIT_LOOP:\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 20000;\n"
+      "  @p bra T3_WAIT_DONE;\n"
+      "  add.u32 c, c, 1;\n"
+      "  setp.lt.u32 q, c, %3;\n"
+      "  @q bra T3_WAIT_LOOP;\n"
+      "T3_WAIT_DONE:\n"
+      "  selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kT3WaitTries)
+      : "memory");
+  return ok != 0;
+}
+// lane 0 of the warp arrives; the others fall through (predicated, no branch)
+__device__ __forceinline__ void t3_mbar_arrive_lane0(unsigned bar, int lane) {
+  asm volatile(
+      "{\n"
+      "  .reg .pred p;\n"
+      "  setp.eq.s32 p, %1, 0;\n"
+      "  @p mbarrier.arrive.shared::cta.b64 _, [%0];\n"
+      "}\n" ::"r"(bar), "r"(lane)
+      : "memory");
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kT3Threads)
+// NP = voxel pairs per thread: pair q sits 16*q output rows below pair 0, so a CTA covers a
+// 32 (w) x 16*NP (h) tile.  More work per thread spreads the per-depth control (table read, ring
+// hand-shake, loop) over more voxels.
+template <typename T, int NP>
+__global__ void __launch_bounds__(kT3Threads, 3)
 resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constant__ T3Maps maps) {
   typedef Ar<T> A;
   typedef P2<T> Q;
   typedef typename Q::V V;
   extern __shared__ __align__(128) unsigned char t3_dyn[];
-  unsigned char* ring = t3_dyn;  // kT3RingBytes, 128-byte aligned
-  T3Shared<T>& sh = *reinterpret_cast<T3Shared<T>*>(t3_dyn + kT3RingBytes);
+  unsigned char* ring = t3_dyn;  // L.ring_bytes, 128-byte aligned
+  T3Shared<T>& sh = *reinterpret_cast<T3Shared<T>*>(t3_dyn + L.ring_bytes);
 
-  const S3Cta k = s3_cta(p, L);
+  const S3Cta k = s3_cta(p, L);  // k.th counts tiles of 16*NP rows here
   if (threadIdx.x == 0) {
     sh.box[0] = 0x7fffffff; sh.box[1] = -0x7fffffff; sh.box[2] = 0x7fffffff; sh.box[3] = -0x7fffffff;
     sh.abort_flag = 0;
-    sh.starts = 0;
-    sh.ok = 1;
   }
   s3_prologue<T>(p, k, sh.s3);  // ends with __syncthreads()
   const RoiGeom<T>& g = sh.s3.g;
   const bool bad_batch = (g.batch < 0 || g.batch >= p.N);
-  if (!sh.s3.zsep || bad_batch) {  // CTA-uniform
-    if (threadIdx.x < kS3Threads) s3_body_l1<T>(p, L, k, sh.s3);
+  if (!sh.s3.zsep || bad_batch) {  // CTA-uniform: plain loads, one 16-row sub-tile at a time
+    if (threadIdx.x < kS3Threads) {
+      for (int q = 0; q < NP; ++q) {
+        S3Cta k2 = k;
+        k2.th = k.th * NP + q;
+        if (k2.th * kS3TileH < p.oh) s3_body_l1<T>(p, L, k2, sh.s3);
+      }
+    }
     return;
   }
 
@@ -177,50 +201,58 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool consumer = warp < kS3Threads / 32;
   const int pw0 = k.tw * kS3TileW + (warp & 1) * 16 + (lane & 7) * 2;
-  const int ph = k.th * kS3TileH + (warp >> 1) * 4 + (lane >> 3);
-  const bool active = consumer && (ph < p.oh && pw0 < p.ow);
-  const bool has_b = active && (pw0 + 1 < p.ow);
+  const int ph0 = k.th * (kS3TileH * NP) + (warp >> 1) * 4 + (lane >> 3);
+  const bool col_ok = consumer && pw0 < p.ow;
+  const bool has_b = col_ok && (pw0 + 1 < p.ow);
 
-  // ---- in-plane position, taps and weights of the two voxels: once per thread
-  int x0a = 0, x0b = 0, y0a = 0, y0b = 0;
-  bool ina = false, inb = false;
-  V lx2, hx2, ly2, hy2;
+  // ---- in-plane position, taps and weights of the 2*NP voxels: once per thread
+  int x0a[NP], x0b[NP], y0a[NP], y0b[NP];
+  bool ina[NP], inb[NP], act[NP];
+  V lx2[NP], hx2[NP], ly2[NP], hy2[NP];
   {
-    const int pwa = active ? pw0 : 0, pwb = has_b ? pw0 + 1 : pwa, phc = active ? ph : 0;
     const T sub_x = lattice_sub<T>(g.bin[0], 0, 1), sub_y = lattice_sub<T>(g.bin[1], 0, 1);
+    const int pwa = col_ok ? pw0 : 0, pwb = has_b ? pw0 + 1 : pwa;
     const T xa = A::add(lattice_base<T>(g.start[0], pwa, g.bin[0], fm), sub_x);
     const T xb = A::add(lattice_base<T>(g.start[0], pwb, g.bin[0], fm), sub_x);
-    const T y = A::add(lattice_base<T>(g.start[1], phc, g.bin[1], fm), sub_y);
     const V x2 = Q::make(xa, xb);
-    V rx2, ry2;
-    if (rotated) {
-      rx2 = Q::add(Q::row_xy(Q::dup(g.rot[0]), x2, Q::dup(A::mul(g.rot[1], y))), Q::dup(g.centre[0]));
-      ry2 = Q::add(Q::row_xy(Q::dup(g.rot[3]), x2, Q::dup(A::mul(g.rot[4], y))), Q::dup(g.centre[1]));
-    } else {
-      rx2 = x2;
-      ry2 = Q::dup(y);
+#pragma unroll
+    for (int q = 0; q < NP; ++q) {
+      const int ph = ph0 + q * kS3TileH;
+      act[q] = col_ok && ph < p.oh;
+      const T y = A::add(lattice_base<T>(g.start[1], act[q] ? ph : 0, g.bin[1], fm), sub_y);
+      V rx2, ry2;
+      if (rotated) {
+        rx2 = Q::add(Q::row_xy(Q::dup(g.rot[0]), x2, Q::dup(A::mul(g.rot[1], y))), Q::dup(g.centre[0]));
+        ry2 = Q::add(Q::row_xy(Q::dup(g.rot[3]), x2, Q::dup(A::mul(g.rot[4], y))), Q::dup(g.centre[1]));
+      } else {
+        rx2 = x2;
+        ry2 = Q::dup(y);
+      }
+      AxisTap<T> txa, txb, tya, tyb;
+      ina[q] = act[q] && !(axis_outside<T>(Q::lo(ry2), p.H) || axis_outside<T>(Q::lo(rx2), p.W));
+      inb[q] = act[q] && has_b && !(axis_outside<T>(Q::hi(ry2), p.H) || axis_outside<T>(Q::hi(rx2), p.W));
+      axis_tap<T>(Q::lo(rx2), p.W, txa);
+      axis_tap<T>(Q::hi(rx2), p.W, txb);
+      axis_tap<T>(Q::lo(ry2), p.H, tya);
+      axis_tap<T>(Q::hi(ry2), p.H, tyb);
+      if (p.order == 0) {
+        nearest_axis<T>(txa.l, txa.h); nearest_axis<T>(txb.l, txb.h);
+        nearest_axis<T>(tya.l, tya.h); nearest_axis<T>(tyb.l, tyb.h);
+      }
+      x0a[q] = txa.i0; x0b[q] = txb.i0; y0a[q] = tya.i0; y0b[q] = tyb.i0;
+      lx2[q] = Q::make(txa.l, txb.l); hx2[q] = Q::make(txa.h, txb.h);
+      ly2[q] = Q::make(tya.l, tyb.l); hy2[q] = Q::make(tya.h, tyb.h);
     }
-    AxisTap<T> txa, txb, tya, tyb;
-    ina = active && !(axis_outside<T>(Q::lo(ry2), p.H) || axis_outside<T>(Q::lo(rx2), p.W));
-    inb = has_b && !(axis_outside<T>(Q::hi(ry2), p.H) || axis_outside<T>(Q::hi(rx2), p.W));
-    axis_tap<T>(Q::lo(rx2), p.W, txa);
-    axis_tap<T>(Q::hi(rx2), p.W, txb);
-    axis_tap<T>(Q::lo(ry2), p.H, tya);
-    axis_tap<T>(Q::hi(ry2), p.H, tyb);
-    if (p.order == 0) {
-      nearest_axis<T>(txa.l, txa.h); nearest_axis<T>(txb.l, txb.h);
-      nearest_axis<T>(tya.l, tya.h); nearest_axis<T>(tyb.l, tyb.h);
-    }
-    x0a = txa.i0; x0b = txb.i0; y0a = tya.i0; y0b = tyb.i0;
-    lx2 = Q::make(txa.l, txb.l); hx2 = Q::make(txa.h, txb.h);
-    ly2 = Q::make(tya.l, tyb.l); hy2 = Q::make(tya.h, tyb.h);
   }
 
   // ---- bounding box of the tile's base taps (inside voxels only)
   {
     int xmin = 0x7fffffff, xmax = -0x7fffffff, ymin = 0x7fffffff, ymax = -0x7fffffff;
-    if (ina) { xmin = xmax = x0a; ymin = ymax = y0a; }
-    if (inb) { xmin = min(xmin, x0b); xmax = max(xmax, x0b); ymin = min(ymin, y0b); ymax = max(ymax, y0b); }
+#pragma unroll
+    for (int q = 0; q < NP; ++q) {
+      if (ina[q]) { xmin = min(xmin, x0a[q]); xmax = max(xmax, x0a[q]); ymin = min(ymin, y0a[q]); ymax = max(ymax, y0a[q]); }
+      if (inb[q]) { xmin = min(xmin, x0b[q]); xmax = max(xmax, x0b[q]); ymin = min(ymin, y0b[q]); ymax = max(ymax, y0b[q]); }
+    }
     xmin = __reduce_min_sync(0xffffffffu, xmin); xmax = __reduce_max_sync(0xffffffffu, xmax);
     ymin = __reduce_min_sync(0xffffffffu, ymin); ymax = __reduce_max_sync(0xffffffffu, ymax);
     if (lane == 0 && xmin <= xmax) {
@@ -230,10 +262,13 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
   }
 
   // ---- plane schedule, in parallel over the depths of the chunk.
-  // The distinct source planes are used in a fixed order; a depth needs the newest plane (its z1)
-  // and either the same plane again or the one fetched just before it (its z0).  Thread i compares
-  // depth i with depth i-1, decides how many planes are new (0, 1 or 2), and a prefix sum of
-  // those counts gives each new plane its position in the schedule.
+  // A warp keeps the tap values of two planes in registers: "older" and "newest".  After depth
+  // i-1 they are (z0, z1) of that depth.  Depth i then needs, with (z0, z1) its own planes:
+  //   nothing new          if (z0, z1) equals what is held;
+  //   one new plane (z1)   if z0 is the newest held plane (the usual step along z);
+  //   two new planes       otherwise (first depth, a jump, or any unusual order).
+  // Thread i decides this from depths i-1 and i alone; a prefix sum over the counts gives every
+  // new plane its position in the schedule that the producer follows.
   {
     const int i = threadIdx.x;
     int adv = 0, z_first = 0, z_second = 0;
@@ -242,27 +277,15 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
       T3Ent<T> t;
       t.h = e.h; t.l = e.l; t.flags = 0;
       if (e.inside) {
-        const bool same = (e.z0 == e.z1);
-        bool ok = true;
-        bool prev_in = false;
-        int pz0 = 0, pz1 = 0;
-        if (i > 0) { prev_in = sh.s3.zt[i - 1].inside != 0; pz0 = sh.s3.zt[i - 1].z0; pz1 = sh.s3.zt[i - 1].z1; }
-        if (!prev_in) {
-          adv = same ? 1 : 2;
-          atomicAdd(&sh.starts, 1);
-          z_first = e.z0; z_second = e.z1;
-        } else {
-          const bool n0 = (e.z0 != pz0 && e.z0 != pz1);
-          const bool n1 = !same && (e.z1 != pz0 && e.z1 != pz1);
-          adv = (n0 ? 1 : 0) + (n1 ? 1 : 0);
-          if (same) ok = n0 || (e.z1 == pz1);
-          else if (adv == 1) ok = n1 && (e.z0 == pz1);
-          else if (adv == 0) ok = (e.z1 == pz1) && (e.z0 == pz0) && (pz0 != pz1);
-          z_first = (adv == 2 || same) ? e.z0 : e.z1;
-          z_second = e.z1;
+        adv = 2;
+        if (i > 0 && sh.s3.zt[i - 1].inside) {
+          const int pz0 = sh.s3.zt[i - 1].z0, pz1 = sh.s3.zt[i - 1].z1;
+          if (e.z0 == pz0 && e.z1 == pz1) adv = 0;
+          else if (e.z0 == pz1) adv = 1;
         }
-        if (!ok) sh.ok = 0;
-        t.flags = (unsigned short)(T3_INSIDE | (same ? T3_SAME : 0));
+        z_first = (adv == 2) ? e.z0 : e.z1;
+        z_second = e.z1;
+        t.flags = T3_INSIDE;
       }
       t.adv = (unsigned short)adv;
       sh.ent[i] = t;
@@ -303,8 +326,14 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
     const int need_w = sh.box[1] + 2 - bx0, need_h = sh.box[3] + 2 - by0;
     for (int j = 0; j < maps.n; ++j)
       if (bsel < 0 && need_w <= maps.bw[j] && need_h <= maps.bh[j]) bsel = j;
-    if (bsel < 0 || !sh.ok || sh.starts > 1) {  // footprint exceeds every box, or unusual plane order
-      if (threadIdx.x < kS3Threads) s3_body_l1<T>(p, L, k, sh.s3);
+    if (bsel < 0) {  // the tile's footprint exceeds every box: plain loads
+      if (threadIdx.x < kS3Threads) {
+        for (int q = 0; q < NP; ++q) {
+          S3Cta k2 = k;
+          k2.th = k.th * NP + q;
+          if (k2.th * kS3TileH < p.oh) s3_body_l1<T>(p, L, k2, sh.s3);
+        }
+      }
       return;
     }
   }
@@ -312,22 +341,23 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
   const int n_planes = any_inside ? sh.warp_tot[0] + sh.warp_tot[1] + sh.warp_tot[2] + sh.warp_tot[3] : 0;
   const unsigned box_bytes = (unsigned)(bw * bh * esz);
   const unsigned stride = (box_bytes + 127u) & ~127u;
-  const int nst = any_inside ? min(kT3MaxStages, (int)(kT3RingBytes / stride)) : 1;
+  const int nst = any_inside ? min(kT3MaxStages, (int)(L.ring_bytes / stride)) : 1;
+  const unsigned ring_s = t3_smem(ring);
+  const unsigned full_s = t3_smem(&sh.full[0]), empty_s = t3_smem(&sh.empty[0]);
 
   if (!consumer) {
     // ================= producer warp: one lane feeds the ring =================
     if (lane != 0) return;
     const int zbase = (g.batch * p.C + k.c) * p.D;  // index of the volume's first plane in (N*C*D)
-    const unsigned ring_s = t3_smem(ring);
     int s = 0;
     unsigned par = 1;  // a fresh "empty" barrier lets the first nst waits through
     int issued = 0;
     bool ok = true;
     for (; issued < n_planes; ++issued) {
-      ok = t3_mbar_wait(&sh.empty[s], par, &sh.abort_flag);
+      ok = t3_mbar_wait(empty_s + 8u * s, par, &sh.abort_flag);
       if (!ok) break;
-      t3_mbar_expect_tx(&sh.full[s], box_bytes);
-      t3_tma_load_3d(ring_s + s * stride, &maps.map[bsel], &sh.full[s], bx0, by0, zbase + sh.plane[issued]);
+      t3_mbar_expect_tx(full_s + 8u * s, box_bytes);
+      t3_tma_load_3d(ring_s + s * stride, &maps.map[bsel], full_s + 8u * s, bx0, by0, zbase + sh.plane[issued]);
       if (++s == nst) { s = 0; par ^= 1u; }
     }
     if (!ok) {
@@ -336,71 +366,107 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
       // stay until this CTA's copies in flight have landed (bounded), so that none writes into
       // shared memory that already belongs to another CTA
       for (int j = max(0, issued - nst); j < issued; ++j)
-        t3_mbar_wait(&sh.full[j % nst], (unsigned)((j / nst) & 1), nullptr);
+        t3_mbar_wait(full_s + 8u * (j % nst), (unsigned)((j / nst) & 1), nullptr);
     }
     return;
   }
 
   // ================= consumer warps =================
   const unsigned row = (unsigned)(bw * esz);
-  const unsigned char* pa = ring + (ina ? ((y0a - by0) * bw + (x0a - bx0)) * esz : 0);
-  const unsigned char* pb = ring + (inb ? ((y0b - by0) * bw + (x0b - bx0)) * esz : 0);
-  const typename Q::M mask = Q::make_mask(ina, inb);
+  unsigned oa[NP], ob[NP];  // shared-memory addresses of the base taps in ring slot 0
+  typename Q::M mask[NP];
+#pragma unroll
+  for (int q = 0; q < NP; ++q) {
+    oa[q] = ring_s + (ina[q] ? (unsigned)(((y0a[q] - by0) * bw + (x0a[q] - bx0)) * esz) : 0u);
+    ob[q] = ring_s + (inb[q] ? (unsigned)(((y0b[q] - by0) * bw + (x0b[q] - bx0)) * esz) : 0u);
+    mask[q] = Q::make_mask(ina[q], inb[q]);
+  }
 
   const long long plane_o = (long long)p.oh * p.ow;
-  T* o = (T*)p.out + k.nc * p.ovol + (long long)k.pd0 * plane_o + (long long)(active ? ph : 0) * p.ow + (active ? pw0 : 0);
-  const bool vec = L.vec_store && has_b;
+  const long long sub_o = (long long)kS3TileH * p.ow;  // output offset between a thread's pairs
+  T* o = (T*)p.out + k.nc * p.ovol + (long long)k.pd0 * plane_o +
+         (long long)(act[0] ? ph0 : 0) * p.ow + (col_ok ? pw0 : 0);
   const V zero2 = Q::dup(A::fi(0));
 
-  int s = 0;
+  unsigned soff = 0;                      // byte offset of the current ring slot
+  unsigned fa = full_s, ea = empty_s;     // its two mbarriers
+  const unsigned ring_end = stride * nst;
   unsigned par = 0;
-  unsigned soff = 0;      // s * stride
-  unsigned newest = 1;    // parity of the schedule position of the newest plane read (starts "odd")
-  V qe[4], qo[4];         // tap values of the planes at even / odd schedule positions
+  // Tap values of the two planes held in registers (lanes = the two voxels): x0y0, x1y0, x0y1,
+  // x1y1.  Which of the two sets is the newest plane alternates with every fetch; `b_newest`
+  // tracks it, and the code below exists once per role assignment, so no register is ever moved.
+  V ra[NP][4], rb[NP][4];
 #pragma unroll
-  for (int t = 0; t < 4; ++t) qe[t] = qo[t] = zero2;
+  for (int q = 0; q < NP; ++q)
+#pragma unroll
+    for (int t = 0; t < 4; ++t) ra[q][t] = rb[q][t] = zero2;
+  bool b_newest = true;
 
-  for (int i = 0; i < npd; ++i, o += plane_o) {
-    const T3Ent<T> e = sh.ent[i];
-    V val = zero2;
-    if ((e.flags & T3_INSIDE) && any_inside) {  // uniform
-      for (int a = 0; a < (int)e.adv; ++a) {
-        if (!t3_mbar_wait(&sh.full[s], par, &sh.abort_flag)) {
-          sh.abort_flag = 1;
-          if (p.status && lane == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
-          return;  // no barrier follows: leaving is safe, the producer drains its copies
-        }
-        newest ^= 1u;
-        if (newest) t3_read_plane<T>(pa + soff, pb + soff, row, qo);
-        else t3_read_plane<T>(pa + soff, pb + soff, row, qe);
-        __syncwarp();
-        if (lane == 0) t3_mbar_arrive(&sh.empty[s]);  // this warp is done with the slot
-        soff += stride;
-        if (++s == nst) { s = 0; soff = 0; par ^= 1u; }
-      }
-      const bool same = (e.flags & T3_SAME) != 0;
-      V acc;
-      if (newest) {
-        V older[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) older[t] = same ? qo[t] : qe[t];
-        acc = t3_interp<T>(e.h, e.l, hy2, ly2, hx2, lx2, older, qo);
-      } else {
-        V older[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) older[t] = same ? qe[t] : qo[t];
-        acc = t3_interp<T>(e.h, e.l, hy2, ly2, hx2, lx2, older, qe);
-      }
-      // output_val = 0 + val (normalises -0), then /count with count == 1
-      val = Q::apply(Q::add(zero2, acc), mask);
-    }
-    if (vec) {
-      Q::store2(o, val);
-    } else if (active) {
-      o[0] = Q::lo(val);
-      if (has_b) o[1] = Q::hi(val);
-    }
+// take the next plane of the schedule out of the ring into register set R
+#define T3_FETCH(R)                                                                       \
+  {                                                                                       \
+    if (!t3_mbar_wait_ptx(fa, par)) {                                                     \
+      sh.abort_flag = 1;                                                                  \
+      if (p.status && lane == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);                  \
+      return; /* no barrier follows: leaving is safe, the producer drains its copies */   \
+    }                                                                                     \
+    _Pragma("unroll") for (int q = 0; q < NP; ++q) {                                      \
+      const unsigned ua = oa[q] + soff, ub = ob[q] + soff;                                \
+      R[q][0] = t3_lds_pair<T>(ua, ub);                                                   \
+      R[q][1] = t3_lds_pair<T>(ua + esz, ub + esz);                                       \
+      R[q][2] = t3_lds_pair<T>(ua + row, ub + row);                                       \
+      R[q][3] = t3_lds_pair<T>(ua + row + esz, ub + row + esz);                           \
+    }                                                                                     \
+    __syncwarp();                                                                         \
+    t3_mbar_arrive_lane0(ea, lane); /* this warp is done with the slot */                 \
+    soff += stride; fa += 8u; ea += 8u;                                                   \
+    if (soff == ring_end) { soff = 0; fa = full_s; ea = empty_s; par ^= 1u; }             \
   }
+
+// the reference's tap sum: older plane OLD supplies taps 1-4, newest plane NEW taps 5-8
+#define T3_COMPUTE(OLD, NEW)                                                              \
+  {                                                                                       \
+    const V hz2 = Q::dup(e.h), lz2 = Q::dup(e.l);                                         \
+    _Pragma("unroll") for (int q = 0; q < NP; ++q) {                                      \
+      const V hzhy = Q::mul(hz2, hy2[q]), hzly = Q::mul(hz2, ly2[q]);                     \
+      const V lzhy = Q::mul(lz2, hy2[q]), lzly = Q::mul(lz2, ly2[q]);                     \
+      V acc = Q::tap_first(Q::mul(hzhy, hx2[q]), OLD[q][0], Q::mul(hzhy, lx2[q]), OLD[q][1]); \
+      acc = Q::tap_next(acc, Q::mul(hzly, hx2[q]), OLD[q][2]);                            \
+      acc = Q::tap_next(acc, Q::mul(hzly, lx2[q]), OLD[q][3]);                            \
+      acc = Q::tap_next(acc, Q::mul(lzhy, hx2[q]), NEW[q][0]);                            \
+      acc = Q::tap_next(acc, Q::mul(lzhy, lx2[q]), NEW[q][1]);                            \
+      acc = Q::tap_next(acc, Q::mul(lzly, hx2[q]), NEW[q][2]);                            \
+      acc = Q::tap_next(acc, Q::mul(lzly, lx2[q]), NEW[q][3]);                            \
+      /* output_val = 0 + val (normalises -0), then /count with count == 1 */             \
+      val[q] = Q::apply(Q::add(zero2, acc), mask[q]);                                     \
+    }                                                                                     \
+  }
+
+#define T3_DEPTH_LOOP(STORE)                                                              \
+  for (int i = 0; i < npd; ++i, o += plane_o) {                                           \
+    const T3Ent<T> e = sh.ent[i];                                                         \
+    V val[NP];                                                                            \
+    _Pragma("unroll") for (int q = 0; q < NP; ++q) val[q] = zero2;                        \
+    if (e.flags && any_inside) { /* uniform */                                            \
+      if (b_newest) {                                                                     \
+        if (e.adv == 1) { T3_FETCH(ra); b_newest = false; T3_COMPUTE(rb, ra); }           \
+        else { if (e.adv == 2) { T3_FETCH(ra); T3_FETCH(rb); } T3_COMPUTE(ra, rb); }      \
+      } else {                                                                            \
+        if (e.adv == 1) { T3_FETCH(rb); b_newest = true; T3_COMPUTE(ra, rb); }            \
+        else { if (e.adv == 2) { T3_FETCH(rb); T3_FETCH(ra); } T3_COMPUTE(rb, ra); }      \
+      }                                                                                   \
+    }                                                                                     \
+    _Pragma("unroll") for (int q = 0; q < NP; ++q) { STORE }                              \
+  }
+
+  if (L.vec_store) {  // even output width and aligned pointer: every stored pair is a vector
+    T3_DEPTH_LOOP(if (act[q]) Q::store2(o + q * sub_o, val[q]);)
+  } else {
+    T3_DEPTH_LOOP(if (act[q]) { T* oq = o + q * sub_o; oq[0] = Q::lo(val[q]); if (has_b) oq[1] = Q::hi(val[q]); })
+  }
+#undef T3_DEPTH_LOOP
+#undef T3_COMPUTE
+#undef T3_FETCH
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -433,10 +499,10 @@ inline bool t3_make_maps(const Params& p, int dtype, T3Maps& m) {
   // boxes in elements, ascending in area; every one fits kT3MaxBoxBytes
   // Box widths keep the row pitch at 8 or 24 (mod 32) four-byte words: the four rows a warp
   // reads then fall into different shared-memory banks.
-  static const int half_boxes[][2] = {{48, 24}, {48, 32}, {48, 40}, {80, 40}, {80, 48}, {112, 48}};
-  static const int float_boxes[][2] = {{40, 24}, {40, 32}, {56, 32}, {56, 40}, {72, 40}};
+  static const int half_boxes[][2] = {{48, 40}, {48, 48}, {80, 40}, {80, 56}, {80, 72}, {112, 56}};
+  static const int float_boxes[][2] = {{40, 40}, {56, 40}, {56, 56}, {72, 40}};
   const int (*boxes)[2] = dtype == 0 ? float_boxes : half_boxes;
-  const int nb = dtype == 0 ? 5 : 6;
+  const int nb = dtype == 0 ? 4 : 6;
   const cuuint64_t gdim[3] = {(cuuint64_t)p.W, (cuuint64_t)p.H, (cuuint64_t)planes};
   const cuuint64_t gstride[2] = {(cuuint64_t)p.W * esz, (cuuint64_t)p.W * p.H * esz};
   const cuuint32_t estride[3] = {1, 1, 1};
@@ -456,7 +522,7 @@ inline bool t3_make_maps(const Params& p, int dtype, T3Maps& m) {
 }
 
 template <typename T>
-inline size_t t3_dynamic_smem() { return (size_t)kT3RingBytes + sizeof(T3Shared<T>); }
+inline size_t t3_dynamic_smem(int ring_bytes) { return (size_t)ring_bytes + sizeof(T3Shared<T>); }
 
 // Picks the streaming kernel when the call has its shape; returns MVR_STREAM3D_NOT_APPLICABLE
 // otherwise (the caller then uses the general kernel).
@@ -468,14 +534,21 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   if (p.ovol < 4096 || p.ow < 8) return MVR_STREAM3D_NOT_APPLICABLE;
   if ((long long)p.H * p.W >= 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
 
+  static const bool use_tma = getenv("MVR_NO_TMA") == nullptr;
+  T3Maps maps;
+  const bool tma = use_tma && t3_make_maps(p, dtype, maps);
+  static const int env_pairs = getenv("MVR_T3_PAIRS") ? atoi(getenv("MVR_T3_PAIRS")) : 0;
+  const int pairs = (env_pairs == 1 || env_pairs == 2) ? env_pairs : kT3Pairs;
+  const int tile_h = tma ? kS3TileH * pairs : kS3TileH;  // output rows per CTA
+
   S3Launch L;
   L.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
-  L.tiles_h = (p.oh + kS3TileH - 1) / kS3TileH;
+  L.tiles_h = (p.oh + tile_h - 1) / tile_h;
   // depth chunk: long enough to amortise the per-thread set-up and to reuse planes, short
   // enough to give every SM several CTAs
   const long long per_depth_ctas = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
   int chunk = kS3MaxChunk;
-  while (chunk > 8 && per_depth_ctas * ((p.od + chunk - 1) / chunk) < 148LL * 12) chunk >>= 1;
+  while (chunk > 8 && per_depth_ctas * ((p.od + chunk - 1) / chunk) < 148LL * 8) chunk >>= 1;
   if (chunk > p.od) chunk = p.od;
   L.chunk = chunk;
   L.chunks = (p.od + chunk - 1) / chunk;
@@ -483,19 +556,23 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   L.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % (2 * esz) == 0);
   const long long ctas = per_depth_ctas * L.chunks;
   if (ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
-  static const bool use_tma = getenv("MVR_NO_TMA") == nullptr;
-  T3Maps maps;
-  if (use_tma && t3_make_maps(p, dtype, maps)) {
+  // ring of plane boxes: what two (NP = 2) or three (NP = 1) resident CTAs per SM can share
+  static const int env_ring = getenv("MVR_T3_RING_KB") ? atoi(getenv("MVR_T3_RING_KB")) : 0;
+  L.ring_bytes = (env_ring > 0 ? env_ring : 60) * 1024;
+  if (tma) {
     // more dynamic shared memory than the default limit: opt in (per function and device)
+#define T3_LAUNCH(TYPE, NP)                                                                                  \
+  {                                                                                                          \
+    cudaFuncSetAttribute(resample_fwd_stream3d_tma<TYPE, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                         (int)t3_dynamic_smem<TYPE>(L.ring_bytes));                                          \
+    resample_fwd_stream3d_tma<TYPE, NP><<<(unsigned)ctas, kT3Threads, t3_dynamic_smem<TYPE>(L.ring_bytes), st>>>(p, L, maps); \
+  }
     if (dtype == 0) {
-      cudaFuncSetAttribute(resample_fwd_stream3d_tma<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)t3_dynamic_smem<float>());
-      resample_fwd_stream3d_tma<float><<<(unsigned)ctas, kT3Threads, t3_dynamic_smem<float>(), st>>>(p, L, maps);
+      if (pairs == 2) T3_LAUNCH(float, 2) else T3_LAUNCH(float, 1)
     } else {
-      cudaFuncSetAttribute(resample_fwd_stream3d_tma<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)t3_dynamic_smem<__half>());
-      resample_fwd_stream3d_tma<__half><<<(unsigned)ctas, kT3Threads, t3_dynamic_smem<__half>(), st>>>(p, L, maps);
+      if (pairs == 2) T3_LAUNCH(__half, 2) else T3_LAUNCH(__half, 1)
     }
+#undef T3_LAUNCH
   } else {
     if (dtype == 0) resample_fwd_stream3d<float><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
     else resample_fwd_stream3d<__half><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
