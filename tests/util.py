@@ -11,7 +11,10 @@ GOLDEN = os.path.join(HERE, "golden", "reference_cuda.npz")
 # A purely relative test is meaningless at zero crossings, so every comparison adds the same
 # fraction of the tensor's rms as absolute slack:  |a - b| <= tol * (|b| + rms(b)).
 FWD_TOL = {torch.float32: 1e-5, torch.float16: 2e-3, torch.float64: 1e-12}
-BWD_TOL = {torch.float32: 1e-4, torch.float16: 2e-2, torch.float64: 1e-11}
+# Half gradients are accumulated by atomics IN HALF, in whatever order the hardware serves them
+# (the reference does the same): two runs of the reference's own kernel differ by several
+# half ulps of the running sum, so the half backward bound is that run-to-run spread.
+BWD_TOL = {torch.float32: 1e-4, torch.float16: 6e-2, torch.float64: 1e-11}
 
 
 def bits(t):
