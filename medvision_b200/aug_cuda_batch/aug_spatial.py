@@ -1,0 +1,303 @@
+"""Batched geometric augmentations built on the resampling op.
+
+Same classes, constructor arguments, parameter draws and roi formulas as the resampling
+transforms of medvision/aug_cuda_batch/aug_spatial.py (Resize :69-194, RandomAffine / Scale /
+Shift / Rotate :355-597, Crop*WithAffine :600-957).  What differs:
+  * the rois of a call are built once (float32 on the host, in the reference's operation order,
+    so the values are the same) and shared by the image and the label fields;
+  * ``times`` crops per image address the SAME image through the roi's batch index instead of
+    concatenating ``times`` copies of the batch;
+  * label fields go through the nearest-neighbour path of the same kernel.
+"""
+import math
+import random
+from typing import Union
+
+import numpy as np
+import torch
+
+from .base import BatchCudaAugBase
+from ..ops.cuda_fun_tools import affine_2d, affine_3d
+
+
+def _resample_fields(result, dim, rois, out_size, sampling_ratio, order):
+    fn = affine_2d if dim == 2 else affine_3d
+    out_size = tuple(int(v) for v in out_size)
+    for key in result.get('img_fields', []):
+        image = result[key]
+        assert image.is_cuda, 'image should be cuda'
+        assert image.ndim == dim + 2, 'image should be batch, channel, **dim'
+        result[key] = fn(image, rois.to(image.device, non_blocking=True), out_size, 1.0, sampling_ratio, True, order)
+    for key in result.get('seg_fields', []):
+        image = result[key]
+        assert image.is_cuda, 'image should be cuda'
+        assert image.ndim == dim + 2, 'image should be batch, channel, **dim'
+        seg = fn(image.float(), rois.to(image.device, non_blocking=True), out_size, 1.0, sampling_ratio, True, 0)
+        result[key] = seg.int()
+    for key in result.get('det_fields', []):
+        raise NotImplementedError
+
+
+def _affine_rois(index, center, shape, shifts, scales, rotate, dim):
+    """[index, center - shape * shifts / scales, shape / scales, angles]; rotation about z in 3D."""
+    if dim == 2:
+        angles = rotate
+    else:
+        angles = torch.cat([torch.zeros_like(rotate), torch.zeros_like(rotate), rotate], dim=1)
+    return torch.cat([index, center - shape * shifts / scales, shape / scales, angles], dim=-1)
+
+
+class BatchCudaResize(BatchCudaAugBase):
+    def __init__(self, spacing=None, scale=None, factor=None, order=1):
+        super().__init__()
+        self.always = True
+        self.spacing = spacing
+        self.scale = scale
+        self.factor = factor
+        self.order = order
+        assert sum([spacing is not None, scale is not None, factor is not None]) == 1
+
+    def __repr__(self):
+        return self.__class__.__name__ + '(spacing={}, scale={}, factor={})'.format(self.spacing, self.scale, self.factor)
+
+    @property
+    def canBackward(self):
+        return True
+
+    def _forward_params(self, result):
+        self._init_params(result)
+        if self.spacing is not None:
+            assert len(self.spacing) == self.dim, f"not match with a {result['img_dim']}D image"
+            img_spacing = np.array(result['img_spacing'])
+            new_spacing = np.array(self.spacing)
+            new_spacing = np.where(new_spacing == -1, img_spacing, new_spacing)
+            scale_factor = tuple(img_spacing / new_spacing)
+        elif self.scale is not None:
+            assert len(self.scale) == self.dim, f"not match with a {result['img_dim']}D image"
+            new_shape = np.array(self.scale)
+            new_shape = np.where(new_shape == -1, self.image_shape, new_shape)
+            scale_factor = tuple(new_shape / self.image_shape)
+        else:
+            assert len(self.factor) == self.dim, f"not match with a {result['img_dim']}D image"
+            scale_factor = tuple(self.factor)
+        self.params = scale_factor
+        result[self.key_name] = self.params
+
+    def _backward_params(self, result):
+        self._init_params(result)
+        params = result.pop(self.key_name, None)
+        if params:
+            self.params = tuple(1 / np.array(params))
+
+    def _rois(self):
+        index = torch.arange(self.batch, dtype=torch.float32).unsqueeze(-1)
+        center = torch.tensor([i / 2 for i in self.image_shape[::-1]], dtype=torch.float32)  # dhw => xyz
+        shape = torch.tensor(list(self.image_shape[::-1]), dtype=torch.float32)
+        angles = torch.zeros(1 if self.dim == 2 else 3)
+        boxes = torch.cat([center, shape, angles]).unsqueeze(0).repeat(self.batch, 1)
+        return torch.cat([index, boxes], dim=-1)
+
+    def apply_to_img(self, result):
+        # the whole image is one roi; image and label fields share it
+        if all(i == 1.0 for i in self.params):
+            return
+        out_size = tuple(int(i * p) for i, p in zip(self.image_shape, self.params))
+        _resample_fields(result, self.dim, self._rois(), out_size, 1, self.order)
+
+    def apply_to_seg(self, result):
+        pass  # done together with the images
+
+
+class BatchCudaRandomAffine(BatchCudaAugBase):
+    def __init__(self, p, scale: Union[float, list, tuple], shift: Union[float, list, tuple],
+                 rotate: Union[float, list, tuple], sampling_ratio=1, order=1):
+        super().__init__()
+        self.p = p
+        self.scale = scale
+        self.shift = shift
+        self.rotate = rotate  # degrees, in the xy plane
+        self.sampling_ratio = sampling_ratio
+        self.order = order
+
+    def __repr__(self):
+        return self.__class__.__name__ + '(dim={}, scale={}, shift={}, rotate={})'.format(
+            self.dim, self.scale, self.shift, self.rotate)
+
+    def _forward_params(self, result):
+        self._init_params(result)
+        scales, shifts, rotate = [], [], []
+        for _ in range(self.batch):
+            scales.append([self.get_range(self.scale, 1), ] * self.dim)
+            shifts.append([self.get_range(self.shift, 0) for _ in range(self.dim)])
+            rotate.append([math.pi * self.get_range(self.rotate, 0) / 180])
+        self.params = {"scales": np.array(scales), "shifts": np.array(shifts), "rotate": np.array(rotate)}
+        result[self.key_name] = self.params
+
+    def _backward_params(self, result: dict):
+        self._init_params(result)
+        params = result.get(self.key_name, None)
+        if params:
+            self.params = {"scales": 1 / params["scales"], "shifts": -params["shifts"], "rotate": -params["rotate"]}
+
+    def _rois(self):
+        scales = torch.FloatTensor(self.params["scales"])
+        shifts = torch.FloatTensor(self.params["shifts"])
+        rotate = torch.FloatTensor(self.params["rotate"])
+        index = torch.arange(self.batch, dtype=torch.float32).unsqueeze(-1)
+        center = torch.tensor([i / 2 for i in self.image_shape[::-1]], dtype=torch.float32)
+        shape = torch.tensor(list(self.image_shape[::-1]), dtype=torch.float32)
+        return _affine_rois(index, center, shape, shifts, scales, rotate, self.dim)
+
+    def apply_to_img(self, result: dict):
+        _resample_fields(result, self.dim, self._rois(), self.image_shape, self.sampling_ratio, self.order)
+
+    def apply_to_seg(self, result: dict):
+        pass  # done together with the images
+
+
+class BatchCudaRandomScale(BatchCudaRandomAffine):
+    def __init__(self, p, scale: Union[float, list, tuple], sampling_ratio=1):
+        super().__init__(p, scale=scale, shift=0, rotate=0, sampling_ratio=sampling_ratio)
+
+
+class BatchCudaRandomShift(BatchCudaRandomAffine):
+    def __init__(self, p, shift: Union[float, list, tuple], sampling_ratio=1):
+        super().__init__(p, scale=0, shift=shift, rotate=0, sampling_ratio=sampling_ratio)
+
+
+class BatchCudaRandomRotate(BatchCudaRandomAffine):
+    def __init__(self, p, rotate: Union[float, list, tuple], sampling_ratio=1):
+        super().__init__(p, scale=0, shift=0, rotate=rotate, sampling_ratio=sampling_ratio)
+
+
+class BatchCudaCropRandomWithAffine(BatchCudaAugBase):
+    def __init__(self, patch_size, scale: Union[float, list, tuple], shift: Union[float, list, tuple],
+                 rotate: Union[float, list, tuple], sampling_ratio=1, order=1, times=1):
+        super().__init__()
+        self.always = True
+        self.dim = len(patch_size)
+        self.patch_size = patch_size
+        self.scale = scale
+        self.shift = shift
+        self.rotate = rotate
+        self.sampling_ratio = sampling_ratio
+        self.order = order
+        self.times = times
+
+    def __repr__(self):
+        return self.__class__.__name__ + "(patch_size={})".format(self.patch_size)
+
+    @property
+    def repeats(self):
+        return self.times
+
+    def _init_params(self, result):
+        super()._init_params(result)
+        self.n_images = self.batch
+        self.batch = self.n_images * self.times  # one parameter set per produced patch
+
+    def _forward_params(self, result):
+        self._init_params(result)
+        assert self.dim == len(self.patch_size)
+        assert all(self.image_shape[i] >= self.patch_size[i] for i in range(self.dim)), self.image_shape
+        batch_start, batch_end = self._forward_crop_params(result)
+        batch_scales, batch_shifts, batch_rotate = self._forward_affine_params(result)
+        self.params = {"start": batch_start, "end": batch_end,  # xyz
+                       "scales": batch_scales, "shifts": batch_shifts, "rotate": batch_rotate}
+        result[self.key_name] = self.params
+
+    def _forward_affine_params(self, result: dict):
+        scales, shifts, rotate = [], [], []
+        for _ in range(self.batch):
+            scales.append([self.get_range(self.scale, 1), ] * self.dim)
+            shifts.append([self.get_range(self.shift, 0) for _ in range(self.dim)])
+            rotate.append([math.pi * self.get_range(self.rotate, 0) / 180])
+        return np.array(scales), np.array(shifts), np.array(rotate)
+
+    def _random_start(self):
+        return tuple(map(lambda a, da: np.random.randint(0, a - da + 1), self.image_shape, self.patch_size))
+
+    def _start_near(self, obj):
+        """a patch start such that the patch covers the object ``obj`` (slices, dhw) with a border"""
+        lo = tuple(min(max(obj[d].stop + self.border - self.patch_size[d], 0), self.image_shape[d] - self.patch_size[d])
+                   for d in range(len(obj)))
+        hi = tuple(min(max(obj[d].start - self.border, 0), self.image_shape[d] - self.patch_size[d])
+                   for d in range(len(obj)))
+        return tuple(map(lambda a, da: np.random.randint(min(a, da), max(a, da) + 1), lo, hi))
+
+    def _collect(self, starts):
+        batch_start = [s[::-1] for s in starts]
+        batch_end = [tuple(a + b for a, b in zip(s, self.patch_size))[::-1] for s in starts]
+        return np.array(batch_start), np.array(batch_end)
+
+    def _forward_crop_params(self, result: dict):
+        return self._collect([self._random_start() for _ in range(self.batch)])
+
+    def _rois(self):
+        start = torch.FloatTensor(self.params["start"])
+        end = torch.FloatTensor(self.params["end"])
+        scales = torch.FloatTensor(self.params["scales"])
+        shifts = torch.FloatTensor(self.params["shifts"])
+        rotate = torch.FloatTensor(self.params["rotate"])
+        # patch r*B + b is cut from image b
+        index = (torch.arange(self.batch) % self.n_images).float().unsqueeze(-1)
+        return _affine_rois(index, (start + end) / 2, end - start, shifts, scales, rotate, self.dim)
+
+    def apply_to_img(self, result: dict):
+        _resample_fields(result, self.dim, self._rois(), self.patch_size, self.sampling_ratio, self.order)
+
+    def apply_to_seg(self, result: dict):
+        pass  # done together with the images
+
+
+class BatchCudaCropCenterWithAffine(BatchCudaCropRandomWithAffine):
+    def _forward_crop_params(self, result: dict):
+        start = tuple(map(lambda a, da: a // 2 - da // 2, self.image_shape, self.patch_size))
+        return self._collect([start for _ in range(self.batch)])
+
+
+class BatchCudaCropForegroundWithAffine(BatchCudaCropRandomWithAffine):
+    def __init__(self, border=12, **kwargs):
+        super().__init__(**kwargs)
+        self.border = border
+
+    def _forward_crop_params(self, result: dict):
+        import scipy.ndimage as ndi
+        assert 'gt_seg' in result.keys() or 'pseudo_mask' in result.keys()
+        mask = result['gt_seg'] if 'gt_seg' in result.keys() else result['pseudo_mask']
+        starts = []
+        for i in range(self.batch):
+            foreground = mask[i % self.n_images, 0]
+            if torch.is_tensor(foreground):
+                foreground = foreground.cpu().numpy()
+            objs = ndi.find_objects(ndi.label(foreground)[0])
+            starts.append(self._start_near(random.choice(objs)) if len(objs) else self._random_start())
+        return self._collect(starts)
+
+
+class BatchCudaCropDetWithAffine(BatchCudaCropRandomWithAffine):
+    """patches around the ground-truth boxes, one box after the other over the repeats"""
+
+    def __init__(self, border=12, **kwargs):
+        super().__init__(**kwargs)
+        self.border = border
+        self.current_repeat_idx = 0
+
+    def _box(self, result, k):
+        obj = result['gt_det'][k]
+        return [slice(int(obj[self.dim - i - 1]), int(obj[2 * self.dim - i - 1])) for i in range(self.dim)]
+
+    def _forward_crop_params(self, result: dict):
+        assert 'gt_det' in result.keys(), "it only used for detection tasks"
+        starts = []
+        for _ in range(self.batch):
+            k = min(self.current_repeat_idx % self.repeats, len(result['gt_det']) - 1)
+            self.current_repeat_idx += 1
+            starts.append(self._start_near(self._box(result, k)))
+        return self._collect(starts)
+
+
+class BatchCudaCropFirstDetWithAffine(BatchCudaCropDetWithAffine):
+    def _forward_crop_params(self, result: dict):
+        assert 'gt_det' in result.keys(), "it only used for detection tasks"
+        return self._collect([self._start_near(self._box(result, 0)) for _ in range(self.batch)])

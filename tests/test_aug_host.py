@@ -1,0 +1,105 @@
+"""Host logic of the batched augmentations (no GPU): parameter draws and roi construction follow
+medvision/aug_cuda_batch/aug_spatial.py."""
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from medvision_b200.aug_cuda_batch import (BatchCudaCropCenterWithAffine, BatchCudaCropRandomWithAffine,
+                                           BatchCudaRandomAffine, BatchCudaRandomRotate, BatchCudaRandomScale,
+                                           BatchCudaRandomShift, BatchCudaResize)
+
+
+def _result(shape=(3, 1, 8, 10, 12)):
+    return {"img_dim": len(shape) - 2, "img": torch.zeros(shape), "img_fields": ["img"], "seg_fields": []}
+
+
+def test_resize_roi_is_the_whole_image():
+    t = BatchCudaResize(factor=(0.5, 0.5, 0.25))
+    res = _result()
+    t._forward_params(res)
+    rois = t._rois()
+    assert rois.shape == (3, 10)
+    assert rois[:, 0].tolist() == [0, 1, 2]
+    # xyz order: centre = shape / 2, size = shape, no rotation
+    assert torch.equal(rois[0, 1:], torch.tensor([6., 5., 4., 12., 10., 8., 0., 0., 0.]))
+    assert res["BatchCudaResize_params"] == (0.5, 0.5, 0.25)
+    t2 = BatchCudaResize(scale=(4, -1, 6))
+    t2._forward_params(_result())
+    assert t2.params == (0.5, 1.0, 0.5)
+    t2._backward_params({"img_dim": 3, "img": torch.zeros(3, 1, 4, 10, 6), "BatchCudaResize_params": t2.params})
+    assert t2.params == (2.0, 1.0, 2.0)
+
+
+def test_random_affine_draws_and_roi_formula():
+    np.random.seed(7)
+    t = BatchCudaRandomAffine(1.0, scale=0.2, shift=0.1, rotate=30)
+    res = _result()
+    t._forward_params(res)
+    # the same draws, in the reference's order: per sample scale, dim shifts, rotation
+    np.random.seed(7)
+    for b in range(3):
+        sc = 1 + np.random.uniform(-0.2, 0.2)
+        sh = [np.random.uniform(-0.1, 0.1) for _ in range(3)]
+        ro = math.pi * np.random.uniform(-30, 30) / 180
+        assert np.allclose(t.params["scales"][b], [sc] * 3)
+        assert np.allclose(t.params["shifts"][b], sh)
+        assert np.allclose(t.params["rotate"][b], [ro])
+    rois = t._rois()
+    shape = np.array([12., 10., 8.], dtype=np.float32)
+    for b in range(3):
+        sc = t.params["scales"][b].astype(np.float32)
+        sh = t.params["shifts"][b].astype(np.float32)
+        want_c = shape / 2 - shape * sh / sc
+        want_s = shape / sc
+        assert np.array_equal(rois[b, 1:4].numpy(), want_c.astype(np.float32))
+        assert np.array_equal(rois[b, 4:7].numpy(), want_s.astype(np.float32))
+        assert rois[b, 7] == 0 and rois[b, 8] == 0  # rotation about z only
+        assert rois[b, 9] == np.float32(t.params["rotate"][b, 0])
+    # inverse parameters
+    t._backward_params(res)
+    assert np.allclose(t.params["scales"], 1 / res["BatchCudaRandomAffine_params"]["scales"])
+
+
+def test_single_purpose_subclasses():
+    np.random.seed(1)
+    t = BatchCudaRandomShift(1.0, shift=0.2)
+    t._forward_params(_result())
+    assert np.all(t.params["scales"] == 1) and np.all(t.params["rotate"] == 0)
+    t = BatchCudaRandomScale(1.0, scale=0.2)
+    t._forward_params(_result())
+    assert np.all(t.params["shifts"] == 0) and np.all(t.params["rotate"] == 0)
+    t = BatchCudaRandomRotate(1.0, rotate=10)
+    t._forward_params(_result((2, 1, 9, 9)))
+    assert t._rois().shape == (2, 6)
+
+
+def test_probability_gate_uses_random_random():
+    random.seed(3)
+    t = BatchCudaRandomRotate(0.0001, rotate=10)
+    res = _result()
+    t._forward(t._pre_forward(res))  # almost surely skipped: nothing is applied, no params stored
+    assert "BatchCudaRandomRotate_params" not in res
+
+
+def test_crop_times_share_the_images():
+    np.random.seed(11)
+    t = BatchCudaCropRandomWithAffine(patch_size=(4, 6, 6), scale=0.1, shift=0, rotate=20, times=4)
+    res = _result()
+    t._forward_params(res)
+    rois = t._rois()
+    assert rois.shape == (12, 10)
+    # patch r*B + b comes from image b: what concatenating `times` copies of the batch would give
+    assert rois[:, 0].tolist() == [0, 1, 2] * 4
+    start, end = t.params["start"], t.params["end"]
+    assert np.all(end - start == np.array([6, 6, 4]))  # xyz
+    assert np.all(start >= 0) and np.all(end <= np.array([12, 10, 8]))
+    sc = torch.FloatTensor(t.params["scales"])
+    assert torch.equal(rois[:, 4:7], torch.FloatTensor(end - start) / sc)
+    t = BatchCudaCropCenterWithAffine(patch_size=(4, 6, 6), scale=0, shift=0, rotate=0)
+    t._forward_params(_result())
+    assert np.all(t.params["start"] == np.array([3, 2, 2]))
+    with pytest.raises(AssertionError):
+        BatchCudaCropRandomWithAffine(patch_size=(40, 6, 6), scale=0, shift=0, rotate=0)._forward_params(_result())

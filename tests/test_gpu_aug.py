@@ -1,0 +1,86 @@
+"""The batched augmentations end to end on the GPU, against the CPU restatement run on the rois
+the transform built."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import port
+from util import n_mismatch
+
+pytestmark = pytest.mark.gpu
+
+
+def _result(shape, dtype, seed, seg=True):
+    g = torch.Generator().manual_seed(seed)
+    img = torch.rand(shape, generator=g).to(dtype).cuda()
+    res = {"img_dim": len(shape) - 2, "img": img, "img_fields": ["img"], "seg_fields": []}
+    if seg:
+        res["gt_seg"] = torch.randint(0, 5, shape, generator=g, dtype=torch.int32).cuda()
+        res["seg_fields"] = ["gt_seg"]
+    return res
+
+
+def _check(t, res_in, out_size, sampling_ratio=1):
+    img_in, seg_in = res_in["img"].clone(), res_in["gt_seg"].clone()
+    res = t(res_in)
+    rois = t._rois()
+    trig = port.device_trig(rois.to(img_in.dtype))
+    want = port.forward(img_in.cpu(), rois, out_size, port.KIND_ROTATED, 1.0, sampling_ratio, True, t.order,
+                        trig=trig, fma_mode=0 if img_in.dtype == torch.float16 else REF_FM)
+    assert n_mismatch(res["img"], want) == 0
+    want_seg = port.forward(seg_in.float().cpu(), rois, out_size, port.KIND_ROTATED, 1.0, 1, True, 0,
+                            trig=port.device_trig(rois), fma_mode=REF_FM).int()
+    assert res["gt_seg"].dtype == torch.int32
+    assert torch.equal(res["gt_seg"].cpu(), want_seg)
+    assert res["history"][-1] == t.name and t.key_name in res
+    return res
+
+
+REF_FM = 1 | (1 << 1) | (1 << 2) | (1 << 3) | (1 << 5) | (1 << 7) | (1 << 10) | (1 << 13) | \
+    (1 << 16) | (1 << 18) | (2 << 20) | (1 << 22)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_resize(dtype):
+    from medvision_b200.aug_cuda_batch import BatchCudaResize
+    t = BatchCudaResize(factor=(0.5, 0.75, 0.5), order=1)
+    res = _check(t, _result((2, 1, 16, 24, 32), dtype, 1), (8, 18, 16))
+    assert res["img"].shape == (2, 1, 8, 18, 16)
+    # a factor of one leaves the fields untouched
+    r2 = _result((1, 1, 8, 8, 8), dtype, 2)
+    before = r2["img"]
+    assert BatchCudaResize(factor=(1.0, 1.0, 1.0))(r2)["img"] is before
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_random_affine_3d_and_2d(dtype):
+    from medvision_b200.aug_cuda_batch import BatchCudaRandomAffine
+    np.random.seed(3)
+    t = BatchCudaRandomAffine(1.0, scale=0.2, shift=0.1, rotate=25)
+    _check(t, _result((3, 2, 12, 24, 32), dtype, 3), (12, 24, 32))
+    t = BatchCudaRandomAffine(1.0, scale=0.2, shift=0.1, rotate=25, sampling_ratio=2)
+    res = _result((3, 2, 20, 24), dtype, 4)
+    img_in = res["img"].clone()
+    out = t(res)
+    rois = t._rois()
+    want = port.forward(img_in.cpu(), rois, (20, 24), port.KIND_ROTATED, 1.0, 2, True, 1,
+                        trig=port.device_trig(rois.to(dtype)), fma_mode=0 if dtype == torch.float16 else REF_FM)
+    assert n_mismatch(out["img"], want) == 0
+
+
+def test_crop_with_affine_times_equals_replicated_batch():
+    from medvision_b200.aug_cuda_batch import BatchCudaCropRandomWithAffine
+    from medvision_b200.ops import affine_3d
+    np.random.seed(5)
+    t = BatchCudaCropRandomWithAffine(patch_size=(8, 16, 16), scale=0.1, shift=0, rotate=20, times=3)
+    res = _result((2, 1, 20, 40, 48), torch.float16, 5)
+    img_in = res["img"].clone()
+    out = _check(t, res, (8, 16, 16))
+    assert out["img"].shape == (6, 1, 8, 16, 16)
+    # the reference's way: concatenate `times` copies and give every copy its own roi
+    rois = t._rois()
+    rep = torch.cat([img_in] * 3)
+    rois_rep = rois.clone()
+    rois_rep[:, 0] = torch.arange(6)
+    want = affine_3d(rep, rois_rep.cuda(), (8, 16, 16), 1.0, 1, True, 1)
+    assert torch.equal(out["img"], want)
