@@ -15,7 +15,9 @@
  *      rotated 2D  (R,6)  [batch, cx, cy, w, h, angle]         medvision/ops/roi_align_rotated_nd.py:171-175
  *      rotated 3D  (R,10) [batch, cx, cy, cz, w, h, d, angle_x, angle_y, angle_z]   (radians)
  *  - Calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
- *    default stream), never synchronise and never allocate.
+ *    default stream) and never synchronise.  The forward entry points allocate nothing.  The
+ *    dense 3D half-precision backward takes a float scratch volume of the gradient's shape from
+ *    the device's stream-ordered memory pool (cudaMallocAsync / cudaFreeAsync on `stream`).
  *  - Return value: MVR_OK or a negative MVR_ERR_* code; nothing is launched on error.
  *    `mvr_strerror` gives the message, worded as the reference's AT_ERROR text where one
  *    exists ("wrong roi size! size_rois should be 10", medvision/csrc/roi_align_rotated_3d.h:34-36).
@@ -79,8 +81,9 @@ int mvr_roi_resample_fwd(const void* features, const void* rois, void* output, i
 
 /* General backward: grad_in += scatter of grad_out * tap weight / sample count.  grad_in has
  * the feature shape, must be zero-filled by the caller (as the reference's Python does,
- * medvision/ops/roi_align_rotated_nd.py:148) and is accumulated into with atomics in the
- * element type, like the reference (medvision/csrc/cuda/roi_align_rotated_3d_cuda_kernel.cuh:251-260).
+ * medvision/ops/roi_align_rotated_nd.py:148) and is accumulated into, like the reference
+ * (medvision/csrc/cuda/roi_align_rotated_3d_cuda_kernel.cuh:251-260): with atomics in the element
+ * type, except that half gradients of dense 3D calls are summed in float and rounded once.
  * Replaces the four backward launchers (medvision/csrc/cuda/roi_align*_cuda.cu:32-55). */
 int mvr_roi_resample_bwd(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim, int roi_kind,
                          int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,

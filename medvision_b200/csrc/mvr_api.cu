@@ -7,6 +7,7 @@
 #include "../../include/mvr.h"
 #include "mvr_generic.cuh"
 #include "mvr_tma3d.cuh"
+#include "mvr_bwd3d.cuh"
 
 namespace {
 
@@ -77,8 +78,8 @@ int launch_mark(const Params& p, cudaStream_t st) {
 
 int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
   if (p.R == 0 || p.C == 0) return MVR_OK;
-  if (fwd) {
-    int rc = try_launch_stream3d(p, dtype, st);
+  {
+    const int rc = fwd ? try_launch_stream3d(p, dtype, st) : try_launch_bwd_stream3d(p, dtype, st);
     if (rc != MVR_STREAM3D_NOT_APPLICABLE) return rc;
   }
   switch (dtype) {

@@ -149,6 +149,40 @@ def test_streaming_kernel_matches_restatement_and_reference(dtype, kind, rot, or
         assert n_mismatch(out, r) == 0, "bit-exact against the reference's own kernel"
 
 
+BWD_STREAM = [(dt, kind, rot, order) for dt in (torch.float16, torch.float32)
+              for kind, rot in ((cases.KIND_ROTATED, "none"), (cases.KIND_ROTATED, "z"), (cases.KIND_ROTATED, "xyz"),
+                                (cases.KIND_BOX, "none")) for order in (1, 0)]
+
+
+@pytest.mark.parametrize("dtype,kind,rot,order", BWD_STREAM,
+                         ids=["%s-%s-%s-o%d" % (str(s[0])[6:], "rot" if s[1] else "box", s[2], s[3]) for s in BWD_STREAM])
+def test_streaming_backward(dtype, kind, rot, order):
+    out_size, spatial = (17, 18, 40), (12, 20, 33)
+    feat, rois = dense_case(kind, dtype, rot, order, out_size, spatial, seed=31 + order + len(rot))
+    g = torch.Generator().manual_seed(77)
+    grad = torch.randn((rois.size(0), feat.size(1)) + out_size, generator=g).to(dtype)
+    kw = dict(spatial_scale=1.0, sampling_ratio=1, aligned=True, order=order)
+    gin = lib_backward(grad.cuda(), rois.cuda(), feat.shape, kind, **kw)
+    trig = port.device_trig(rois) if kind == cases.KIND_ROTATED else None
+    fm = REF_FM if dtype == torch.float32 else 0
+    # every product grad*w is formed as the reference forms it; only the order (and for half the
+    # width) of the summation differs: compare with the wide-accumulator restatement tightly ...
+    wide = port.backward(grad, rois, feat.shape, kind, trig=trig, fma_mode=fm, wide_acc=True, **kw)
+    assert_close(gin, wide, 2e-3 if dtype == torch.float16 else 1e-5, "vs wide accumulation")
+    # ... and with the reference's element-type accumulation within its own run-to-run spread
+    narrow = port.backward(grad, rois, feat.shape, kind, trig=trig, fma_mode=fm, **kw)
+    assert_close(gin, narrow, BWD_TOL[dtype], "vs element-type accumulation")
+    if ref.available():
+        r = ref.backward(grad.cuda(), rois.cuda(), feat.shape, kind, **kw)
+        assert_close(gin, r, BWD_TOL[dtype], "vs the reference's own kernel")
+    # adjointness against the forward: <fwd(f), g> == <f, bwd(g)>
+    if dtype == torch.float32:
+        out = lib_forward(feat.cuda(), rois.cuda(), out_size, kind, **kw)
+        lhs = float((out.double().cpu() * grad.double()).sum())
+        rhs = float((feat.double() * gin.double().cpu()).sum())
+        assert abs(lhs - rhs) <= 1e-4 * max(1.0, abs(lhs))
+
+
 def test_streaming_kernel_unaligned_output_pointer():
     feat, rois = dense_case(cases.KIND_ROTATED, torch.float16, "z", 1, (16, 16, 32), (10, 12, 14), seed=5)
     kw = dict(spatial_scale=1.0, sampling_ratio=1, aligned=True, order=1)
