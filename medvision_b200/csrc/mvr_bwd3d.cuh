@@ -154,17 +154,13 @@ __global__ void bwd_fold_half(__half* __restrict__ grad_in, const float* __restr
   }
 }
 
-// Launches the streaming backward when the call has its shape (3D, one sample per voxel, half or
-// float in the reference's contraction pattern); MVR_STREAM3D_NOT_APPLICABLE otherwise.
-// Half needs a float scratch volume: it is taken from the stream-ordered memory pool and
-// returned to it on the same stream.
-inline int try_launch_bwd_stream3d(const Params& p, int dtype, cudaStream_t st) {
-  if (p.ndim != 3 || p.sampling_ratio != 1) return MVR_STREAM3D_NOT_APPLICABLE;
-  if (dtype != 0 && dtype != 1) return MVR_STREAM3D_NOT_APPLICABLE;
-  if (dtype == 0 && p.fm != kS3FloatPattern) return MVR_STREAM3D_NOT_APPLICABLE;
-  if (p.ovol < 4096 || p.ow < 8) return MVR_STREAM3D_NOT_APPLICABLE;
-  if ((long long)p.H * p.W >= 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
-  S3Launch L;
+// Shape test and launch geometry of the streaming backward.
+inline bool bwd_stream3d_applicable(const Params& p, int dtype, S3Launch& L, long long& ctas) {
+  if (p.ndim != 3 || p.sampling_ratio != 1) return false;
+  if (dtype != 0 && dtype != 1) return false;
+  if (dtype == 0 && p.fm != kS3FloatPattern) return false;
+  if (p.ovol < 4096 || p.ow < 8) return false;
+  if ((long long)p.H * p.W >= 0x7fffffffLL) return false;
   L.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
   L.tiles_h = (p.oh + kS3TileH - 1) / kS3TileH;
   const long long per_depth_ctas = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
@@ -175,8 +171,30 @@ inline int try_launch_bwd_stream3d(const Params& p, int dtype, cudaStream_t st) 
   L.chunks = (p.od + chunk - 1) / chunk;
   L.vec_store = 0;
   L.ring_bytes = 0;
-  const long long ctas = per_depth_ctas * L.chunks;
-  if (ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
+  ctas = per_depth_ctas * L.chunks;
+  return ctas <= 0x7fffffffLL;
+}
+
+// Half backward through a float scratch volume of n = N*C*D*H*W elements that the caller of this
+// function owns: clear it, scatter into it, fold it into grad_in.  Allocates nothing.
+inline int launch_bwd_stream3d_half(const Params& p, const S3Launch& L, long long ctas, float* scratch,
+                                    cudaStream_t st) {
+  const long long n = (long long)p.N * p.C * p.vol;
+  cudaMemsetAsync(scratch, 0, (size_t)n * sizeof(float), st);
+  resample_bwd_stream3d<__half><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L, scratch);
+  const long long blocks = (n + 8 * 256 - 1) / (8 * 256);
+  bwd_fold_half<<<(unsigned)blocks, 256, 0, st>>>((__half*)p.out, scratch, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+// Launches the streaming backward when the call has its shape (3D, one sample per voxel, half or
+// float in the reference's contraction pattern); MVR_STREAM3D_NOT_APPLICABLE otherwise.
+// Half needs a float scratch volume: it is taken from the stream-ordered memory pool and
+// returned to it on the same stream.
+inline int try_launch_bwd_stream3d(const Params& p, int dtype, cudaStream_t st) {
+  S3Launch L;
+  long long ctas = 0;
+  if (!bwd_stream3d_applicable(p, dtype, L, ctas)) return MVR_STREAM3D_NOT_APPLICABLE;
   if (dtype == 0) {
     resample_bwd_stream3d<float><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L, (float*)p.out);
     return cudaGetLastError() == cudaSuccess ? 0 : -8;
@@ -187,13 +205,9 @@ inline int try_launch_bwd_stream3d(const Params& p, int dtype, cudaStream_t st) 
     cudaGetLastError();
     return MVR_STREAM3D_NOT_APPLICABLE;  // no memory for the scratch volume: element-type atomics instead
   }
-  cudaMemsetAsync(scratch, 0, (size_t)n * sizeof(float), st);
-  resample_bwd_stream3d<__half><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L, scratch);
-  const long long blocks = (n + 8 * 256 - 1) / (8 * 256);
-  bwd_fold_half<<<(unsigned)blocks, 256, 0, st>>>((__half*)p.out, scratch, n);
-  const cudaError_t e = cudaGetLastError();
+  const int rc = launch_bwd_stream3d_half(p, L, ctas, scratch, st);
   cudaFreeAsync(scratch, st);
-  return e == cudaSuccess ? 0 : -8;
+  return rc;
 }
 
 }  // namespace mvr
