@@ -56,6 +56,8 @@ extern "C" {
 #define MVR_ERR_LAUNCH (-8)
 #define MVR_ERR_TOO_LARGE (-9)
 #define MVR_ERR_NO_DEVICE (-10)
+#define MVR_ERR_SCRATCH_LIMIT (-11)
+#define MVR_ERR_SCRATCH_ADDRESS (-12)
 
 #define MVR_STATUS_BAD_BATCH_INDEX 1
 
@@ -89,6 +91,38 @@ int mvr_roi_resample_bwd(const void* grad_out, const void* rois, void* grad_in, 
                          int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
                          int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
                          int* status, void* stream);
+
+/* Backward for callers that must not allocate device memory.  It has no counterpart in the
+ * reference.
+ *
+ * Same arguments, same result and same error codes as mvr_roi_resample_bwd.  The difference is
+ * where the float accumulator of the dense 3D half-precision backward lives: the regular entry
+ * point borrows it from the stream-ordered memory pool for the duration of the call; this one uses
+ * a fixed array inside the library image and calls no cudaMalloc / cudaFree / pool routine at all
+ * (shapes and element types that need no accumulator volume go to the very same kernels as with
+ * the regular entry point, which never allocated for them either).
+ *
+ * It is meant for hosts where an allocation at call time is not an option: a plug-in whose
+ * run-time hook is forbidden to allocate once initialisation is over, a worker that shares the GPU
+ * with a framework which has already reserved the whole device for its own caching allocator (so
+ * that a foreign allocation fails or fragments it), or a loop with a latency budget that cannot
+ * absorb the implicit synchronisation an allocation may bring.
+ *
+ * Limits and rules
+ *  - The accumulator holds MVR_NOALLOC_MAX_ELEMENTS = 4 194 304 floats (16 MiB).  Every GPU on
+ *    which the library is loaded keeps that memory until the process ends.  A half call whose
+ *    gradient volume N*C*D*H*W exceeds it returns MVR_ERR_SCRATCH_LIMIT and launches nothing.
+ *  - The first call on a device asks the runtime for the array's device address (once per device,
+ *    with that device current); make that first call before any stream capture begins.
+ *  - All calls on a device share the one array.  Each call clears the part it uses on `stream`
+ *    before scattering into it, so earlier contents never leak into a result; but two calls that
+ *    can overlap on the GPU (different streams, no dependency between them) race on it and both
+ *    results are garbage.  Serialise such calls. */
+#define MVR_NOALLOC_MAX_ELEMENTS 4194304
+int mvr_roi_resample_bwd_noalloc(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim,
+                                 int roi_kind, int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R,
+                                 int roi_width, int od, int oh, int ow, float spatial_scale, int sampling_ratio,
+                                 int aligned, int order, int* status, void* stream);
 
 /* Measurement utility; has no counterpart in the reference.  Sets mask[b, c, voxel] = 1 (bytes,
  * feature shape, zero-filled by the caller) for every input element that a tap of the

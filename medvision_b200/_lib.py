@@ -28,6 +28,7 @@ _ROT3D = [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _
 PROTOTYPES = {
     "mvr_roi_resample_fwd": _GENERAL,
     "mvr_roi_resample_bwd": _GENERAL,
+    "mvr_roi_resample_bwd_noalloc": _GENERAL,
     "mvr_roi_resample_touched": [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _i32,
                                  _i32, _i32, _i32, _f32, _i32, _i32, _i32, _vp],
     "mvr_roi_align_2d_forward": _BOX2D,

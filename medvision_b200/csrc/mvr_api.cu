@@ -3,15 +3,45 @@
 #include <cuda_runtime.h>
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include "../../include/mvr.h"
 #include "mvr_generic.cuh"
 #include "mvr_tma3d.cuh"
 #include "mvr_bwd3d.cuh"
 
+// ---- scratch of the entry point that allocates nothing ------------------------------------
+// Lives in the library image: every GPU that loads the library holds these 16 MiB until the
+// process exits.  In host code the name below is only a stand-in for the device array; the
+// device address is asked for once per device (noalloc_scratch_of_current_device).
+static __device__ __align__(256) float g_noalloc_scratch[MVR_NOALLOC_MAX_ELEMENTS];
+
 namespace {
 
 using namespace mvr;
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_addr[kMaxDevices] = {};
+
+// Device address of g_noalloc_scratch on the CURRENT device, looked up on the first call for that
+// device and remembered.
+int noalloc_scratch_of_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MVR_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_addr[dev]) {
+    float* addr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&addr, g_noalloc_scratch);
+    if (e != cudaSuccess || !addr) {
+      cudaGetLastError();
+      return MVR_ERR_SCRATCH_ADDRESS;
+    }
+    g_noalloc_addr[dev] = addr;
+  }
+  *out = g_noalloc_addr[dev];
+  return MVR_OK;
+}
 
 // Float contraction pattern of the reference build (see mvr_arith.cuh).
 // Found by matching the reference's own kernels bit for bit on a B200 (float32, all roi
@@ -106,6 +136,10 @@ const char* mvr_strerror(int code) {
     case MVR_ERR_LAUNCH: return "CUDA kernel launch failed";
     case MVR_ERR_TOO_LARGE: return "problem too large for one launch";
     case MVR_ERR_NO_DEVICE: return "no CUDA device";
+    case MVR_ERR_SCRATCH_LIMIT:
+      return "gradient volume larger than the built-in scratch of mvr_roi_resample_bwd_noalloc "
+             "(4194304 elements): use mvr_roi_resample_bwd, or split the batch";
+    case MVR_ERR_SCRATCH_ADDRESS: return "the device address of the built-in scratch could not be obtained";
     default: return "unknown error";
   }
 }
@@ -149,6 +183,38 @@ int mvr_roi_resample_touched(const void* rois, unsigned char* mask, int dtype, i
     case MVR_F32: return launch_mark<float>(p, (cudaStream_t)stream);
     case MVR_F16: return launch_mark<__half>(p, (cudaStream_t)stream);
     default: return launch_mark<double>(p, (cudaStream_t)stream);
+  }
+}
+
+int mvr_roi_resample_bwd_noalloc(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim,
+                                 int roi_kind, int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R,
+                                 int roi_width, int od, int oh, int ow, float spatial_scale, int sampling_ratio,
+                                 int aligned, int order, int* status, void* stream) {
+  int rc = check_common(grad_out, rois, grad_in, dtype, ndim, roi_kind, N, C, D, H, W, R, roi_width, od, oh, ow, order);
+  if (rc != MVR_OK) return rc;
+  Params p = make_params(grad_out, rois, grad_in, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow, spatial_scale,
+                         sampling_ratio, aligned, order, status);
+  if (p.R == 0 || p.C == 0) return MVR_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  S3Launch L;
+  long long ctas = 0;
+  if (bwd_stream3d_applicable(p, dtype, L, ctas)) {
+    if (dtype == MVR_F32) {  // float gradients are reduced straight into grad_in: no scratch at all
+      resample_bwd_stream3d<float><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L, (float*)p.out);
+      return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
+    }
+    // half: the float accumulator volume is the library's own static array
+    if ((long long)p.N * p.C * p.vol > (long long)MVR_NOALLOC_MAX_ELEMENTS) return MVR_ERR_SCRATCH_LIMIT;
+    float* scratch = nullptr;
+    rc = noalloc_scratch_of_current_device(&scratch);
+    if (rc != MVR_OK) return rc;
+    return launch_bwd_stream3d_half(p, L, ctas, scratch, st) == 0 ? MVR_OK : MVR_ERR_LAUNCH;
+  }
+  // every other shape is served by the element-type-atomics kernel, which has no scratch
+  switch (dtype) {
+    case MVR_F32: return launch_generic<float>(p, false, st);
+    case MVR_F16: return launch_generic<__half>(p, false, st);
+    default: return launch_generic<double>(p, false, st);
   }
 }
 

@@ -1,0 +1,91 @@
+"""The backward entry point that allocates nothing (mvr_roi_resample_bwd_noalloc).
+
+Some hosts of this library cannot allocate device memory at call time -- a plug-in hook that may
+not allocate after initialisation, a worker beside a framework that has reserved the whole GPU
+for its own allocator -- so the half-precision dense 3D backward, which normally borrows a
+float accumulator volume from the memory pool, also exists with that accumulator in a fixed
+array inside the library.  This file checks, through the C ABI, that the variant gives what the
+regular entry point gives, twice in a row (the array is shared and keeps old contents between
+calls), and that it refuses volumes beyond its fixed capacity.
+
+The file name sorts last on purpose: a run that stops at the first failure has then already
+run every other test.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(fn, grad, rois, gin, stream=None):
+    from medvision_b200 import _lib
+    N, C, D, H, W = gin.shape
+    R = rois.size(0)
+    od, oh, ow = grad.shape[2:]
+    code = {torch.float16: _lib.MVR_F16, torch.float32: _lib.MVR_F32}[grad.dtype]
+    st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+    return fn(grad.data_ptr(), rois.data_ptr(), gin.data_ptr(), code, 3, _lib.MVR_ROI_ROTATED, N, C, D, H, W, R,
+              rois.size(1), od, oh, ow, 1.0, 1, 1, 1, None, st)
+
+
+def _job(seed, shape=(2, 2, 24, 40, 48), out=(20, 32, 40), R=5):
+    g = torch.Generator().manual_seed(seed)
+    N, C, D, H, W = shape
+    b = torch.randint(0, N, (R, 1), generator=g).float()
+    ext = torch.tensor([W, H, D], dtype=torch.float32)
+    centre = ext / 2 + (torch.rand(R, 3, generator=g) - 0.5) * ext * 0.4
+    size = ext * (0.6 + 0.6 * torch.rand(R, 3, generator=g))
+    ang = (torch.rand(R, 3, generator=g) - 0.5) * 0.8
+    ang[0] = 0
+    ang[1, :2] = 0
+    rois = torch.cat([b, centre, size, ang], 1).half().cuda()
+    grad = torch.randn((R, C) + out, generator=g).half().cuda()
+    return grad, rois, shape
+
+
+def test_noalloc_backward_equals_regular_backward_twice_in_a_row():
+    from medvision_b200 import _lib
+    L = _lib.lib
+    for rep, seed in enumerate((101, 202)):  # second call: the shared array still holds call one
+        grad, rois, shape = _job(seed)
+        want = torch.zeros(shape, dtype=torch.float16, device="cuda")
+        got = torch.zeros(shape, dtype=torch.float16, device="cuda")
+        assert _call(L.mvr_roi_resample_bwd, grad, rois, want) == 0
+        assert _call(L.mvr_roi_resample_bwd_noalloc, grad, rois, got) == 0
+        torch.cuda.synchronize()
+        assert float(want.abs().max()) > 0
+        # Both sum the same half products in a float accumulator; only the order in which the
+        # reductions land differs, so the tolerance is that of float summation, far below a half ulp.
+        err = (got.float() - want.float()).abs()
+        bound = 2e-3 * (want.float().abs() + float(want.float().pow(2).mean().sqrt()))
+        assert bool((err <= bound).all()), "call %d: max abs err %g" % (rep, float(err.max()))
+
+
+def test_noalloc_backward_serves_the_shapes_without_accumulator_too():
+    from medvision_b200 import _lib
+    L = _lib.lib
+    grad, rois, shape = _job(303)
+    want = torch.zeros(shape, dtype=torch.float32, device="cuda")
+    got = torch.zeros(shape, dtype=torch.float32, device="cuda")
+    assert _call(L.mvr_roi_resample_bwd, grad.float(), rois.float(), want) == 0
+    assert _call(L.mvr_roi_resample_bwd_noalloc, grad.float(), rois.float(), got) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-5)
+
+
+def test_noalloc_backward_refuses_volumes_beyond_its_capacity():
+    from medvision_b200 import _lib
+    L = _lib.lib
+    shape = (1, 1, 129, 256, 128)  # 4 227 072 elements > 4 194 304
+    grad, rois, _ = _job(404, shape=shape, out=(16, 32, 32), R=2)
+    gin = torch.zeros(shape, dtype=torch.float16, device="cuda")
+    rc = _call(L.mvr_roi_resample_bwd_noalloc, grad, rois, gin)
+    assert rc == -11
+    assert "4194304" in _lib.strerror(rc)
+    torch.cuda.synchronize()
+    assert float(gin.abs().max()) == 0.0  # nothing was launched
+    # the regular entry point takes the same call
+    assert _call(L.mvr_roi_resample_bwd, grad, rois, gin) == 0
+    torch.cuda.synchronize()
