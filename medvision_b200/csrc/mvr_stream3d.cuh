@@ -113,6 +113,67 @@ __device__ __forceinline__ void nearest_axis(T& l, T& h) {
   l = (!hh && ll) ? A::fi(1) : A::fi(0);
 }
 
+// One interpolation axis for the two voxels of a pair at once (same results as axis_tap /
+// axis_outside / nearest_axis applied to each lane; `size` must be at most 2048 for half so that
+// it is a half value).
+template <typename T>
+struct AxisTap2 {
+  int i0a, i0b;        // lower tap index per lane
+  int da, db;          // 1 when the upper tap is i0 + 1, 0 when it is clamped onto i0
+  typename P2<T>::V l, h;
+  bool outa, outb;     // coordinate outside [-1, size]: the sample contributes nothing
+};
+
+template <typename T>
+__device__ __forceinline__ void axis_tap2(typename P2<T>::V c, int size, int order, AxisTap2<T>& t);
+
+template <>
+__device__ __forceinline__ void axis_tap2<__half>(__half2 c, int size, int order, AxisTap2<__half>& t) {
+  const __half2 zero = __float2half2_rn(0.0f), one = __float2half2_rn(1.0f);
+  const unsigned out = __hlt2_mask(c, __float2half2_rn(-1.0f)) | __hgt2_mask(c, __float2half2_rn((float)size));
+  t.outa = (out & 0xffffu) != 0;
+  t.outb = (out >> 16) != 0;
+  // `if (c <= 0) c = 0`: a NaN stays a NaN
+  c = __hmax2_nan(c, zero);
+  int ia = __half2int_rz(__low2half(c)), ib = __half2int_rz(__high2half(c));
+  const bool ca = ia >= size - 1, cb = ib >= size - 1;  // upper neighbour clamped onto the last index
+  ia = ca ? size - 1 : ia;
+  ib = cb ? size - 1 : ib;
+  t.i0a = ia; t.i0b = ib;
+  t.da = ca ? 0 : 1; t.db = cb ? 0 : 1;
+  // l = c - (T)i0: i0 = floor(c) for c >= 0; a clamped lane has c := (T)i0, hence l = +0
+  __half2 l = __hsub2_rn(c, h2floor(c));
+  const unsigned keep = (ca ? 0u : 0x0000ffffu) | (cb ? 0u : 0xffff0000u);
+  unsigned lu = *reinterpret_cast<unsigned*>(&l) & keep;
+  l = *reinterpret_cast<__half2*>(&lu);
+  __half2 h = __hsub2_rn(one, l);
+  if (order == 0) {  // one-hot choice per axis: prefer the lower index when h >= .5
+    const __half2 half_ = __float2half2_rn(0.5f);
+    const unsigned hh = __hge2_mask(h, half_);
+    const unsigned ll = __hge2_mask(l, half_) & ~hh;
+    unsigned ou = *reinterpret_cast<const unsigned*>(&one);
+    unsigned hu = ou & hh, l2 = ou & ll;
+    h = *reinterpret_cast<__half2*>(&hu);
+    l = *reinterpret_cast<__half2*>(&l2);
+  }
+  t.l = l;
+  t.h = h;
+}
+
+template <>
+__device__ __forceinline__ void axis_tap2<float>(Float2Lanes c, int size, int order, AxisTap2<float>& t) {
+  AxisTap<float> a, b;
+  t.outa = axis_outside<float>(c.a, size);
+  t.outb = axis_outside<float>(c.b, size);
+  axis_tap<float>(c.a, size, a);
+  axis_tap<float>(c.b, size, b);
+  if (order == 0) { nearest_axis<float>(a.l, a.h); nearest_axis<float>(b.l, b.h); }
+  t.i0a = a.i0; t.i0b = b.i0;
+  t.da = a.i1 - a.i0; t.db = b.i1 - b.i0;
+  t.l = P2<float>::make(a.l, b.l);
+  t.h = P2<float>::make(a.h, b.h);
+}
+
 template <typename T>
 struct S3ZTap {        // z-separable: per output depth
   long long o0, o1;    // element offsets of the two source planes inside the volume
@@ -140,6 +201,93 @@ struct S3Launch {
   int vec_store;                        // 1: two-element vector stores are aligned
   int ring_bytes;                       // TMA-staged kernel: bytes of the shared-memory plane ring
 };
+
+// General-rotation depth loop for NP voxel pairs of one thread (pair q sits q*row_step output
+// rows below pair 0): positions change with depth, so all three axis taps are formed per voxel;
+// the x- and y-products of the rotation are formed once per thread, the z-products once per
+// depth and CTA (S3ZProd table).  Both lanes of a pair go through the same instructions.
+template <typename T, int NP>
+__device__ __forceinline__ void s3_full_depth_loop(const Params& p, const S3Shared<T>& sh, int npd, int c,
+                                                   int pw0, int ph0, int row_step, bool vec_store, T* out0) {
+  typedef Ar<T> A;
+  typedef P2<T> Q;
+  typedef typename Q::V V;
+  const RoiGeom<T>& g = sh.g;
+  const int fm = kS3FloatPattern;
+  const bool has_b = (pw0 + 1 < p.ow);
+  const T* vol = (const T*)p.in + ((long long)g.batch * p.C + c) * p.vol;
+  const V zero2 = Q::dup(A::fi(0));
+  const T sub_x = lattice_sub<T>(g.bin[0], 0, 1), sub_y = lattice_sub<T>(g.bin[1], 0, 1);
+  const T xa = A::add(lattice_base<T>(g.start[0], pw0, g.bin[0], fm), sub_x);
+  const T xb = A::add(lattice_base<T>(g.start[0], has_b ? pw0 + 1 : pw0, g.bin[0], fm), sub_x);
+  const V x2 = Q::make(xa, xb);
+  V sxy[NP][3];
+  bool act[NP];
+#pragma unroll
+  for (int q = 0; q < NP; ++q) {
+    const int ph = ph0 + q * row_step;
+    act[q] = ph < p.oh;
+    const T y = A::add(lattice_base<T>(g.start[1], act[q] ? ph : 0, g.bin[1], fm), sub_y);
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+      sxy[q][r] = Q::row_xy(Q::dup(g.rot[3 * r]), x2, Q::dup(A::mul(g.rot[3 * r + 1], y)));
+  }
+  const V c2[3] = {Q::dup(g.centre[0]), Q::dup(g.centre[1]), Q::dup(g.centre[2])};
+  const int W = p.W, HW = p.H * p.W;
+  const long long plane_o = (long long)p.oh * p.ow;
+  const long long sub_o = (long long)row_step * p.ow;
+  T* o = out0;
+  for (int i = 0; i < npd; ++i, o += plane_o) {
+    const S3ZProd<T> e = sh.zp[i];
+#pragma unroll
+    for (int q = 0; q < NP; ++q) {
+      if (!act[q]) continue;
+      const V rx2 = Q::add(Q::add(sxy[q][0], Q::dup(e.p[0])), c2[0]);
+      const V ry2 = Q::add(Q::add(sxy[q][1], Q::dup(e.p[1])), c2[1]);
+      const V rz2 = Q::add(Q::add(sxy[q][2], Q::dup(e.p[2])), c2[2]);
+      AxisTap2<T> tx, ty, tz;
+      axis_tap2<T>(rx2, p.W, p.order, tx);
+      axis_tap2<T>(ry2, p.H, p.order, ty);
+      axis_tap2<T>(rz2, p.D, p.order, tz);
+      const bool ina = !(tx.outa || ty.outa || tz.outa);
+      const bool inb = has_b && !(tx.outb || ty.outb || tz.outb);
+      // element offsets of the eight taps inside the volume, per lane
+      const int ba = (tz.i0a * p.H + ty.i0a) * W + tx.i0a;
+      const int bb = (tz.i0b * p.H + ty.i0b) * W + tx.i0b;
+      const int dya = ty.da ? W : 0, dyb = ty.db ? W : 0, dza = tz.da ? HW : 0, dzb = tz.db ? HW : 0;
+      const T* pa = vol + (ina ? ba : 0);
+      const T* pb = vol + (inb ? bb : 0);
+      const int xa1 = ina ? tx.da : 0, xb1 = inb ? tx.db : 0;
+      const int ya1 = ina ? dya : 0, yb1 = inb ? dyb : 0, za1 = ina ? dza : 0, zb1 = inb ? dzb : 0;
+      V v[8];
+      v[0] = Q::make(__ldg(pa), __ldg(pb));
+      v[1] = Q::make(__ldg(pa + xa1), __ldg(pb + xb1));
+      v[2] = Q::make(__ldg(pa + ya1), __ldg(pb + yb1));
+      v[3] = Q::make(__ldg(pa + ya1 + xa1), __ldg(pb + yb1 + xb1));
+      v[4] = Q::make(__ldg(pa + za1), __ldg(pb + zb1));
+      v[5] = Q::make(__ldg(pa + za1 + xa1), __ldg(pb + zb1 + xb1));
+      v[6] = Q::make(__ldg(pa + za1 + ya1), __ldg(pb + zb1 + yb1));
+      v[7] = Q::make(__ldg(pa + za1 + ya1 + xa1), __ldg(pb + zb1 + yb1 + xb1));
+      const V hzhy = Q::mul(tz.h, ty.h), hzly = Q::mul(tz.h, ty.l);
+      const V lzhy = Q::mul(tz.l, ty.h), lzly = Q::mul(tz.l, ty.l);
+      V acc = Q::tap_first(Q::mul(hzhy, tx.h), v[0], Q::mul(hzhy, tx.l), v[1]);
+      acc = Q::tap_next(acc, Q::mul(hzly, tx.h), v[2]);
+      acc = Q::tap_next(acc, Q::mul(hzly, tx.l), v[3]);
+      acc = Q::tap_next(acc, Q::mul(lzhy, tx.h), v[4]);
+      acc = Q::tap_next(acc, Q::mul(lzhy, tx.l), v[5]);
+      acc = Q::tap_next(acc, Q::mul(lzly, tx.h), v[6]);
+      acc = Q::tap_next(acc, Q::mul(lzly, tx.l), v[7]);
+      const V val = Q::apply(Q::add(zero2, acc), Q::make_mask(ina, inb));
+      T* oq = o + q * sub_o;
+      if (vec_store && has_b) {
+        Q::store2(oq, val);
+      } else {
+        oq[0] = Q::lo(val);
+        if (has_b) oq[1] = Q::hi(val);
+      }
+    }
+  }
+}
 
 // CTA coordinates of the streaming kernels: tile_w fastest, then tile_h, depth chunk, (roi, channel)
 struct S3Cta {
@@ -347,46 +495,8 @@ __device__ void s3_body_l1(const Params& p, const S3Launch& L, const S3Cta& k, S
     return;
   }
 
-  // ---- general rotation: positions change with depth; x- and y-products are formed once
-  V sxy[3];
-#pragma unroll
-  for (int r = 0; r < 3; ++r)
-    sxy[r] = Q::row_xy(Q::dup(g.rot[3 * r]), x2, Q::dup(A::mul(g.rot[3 * r + 1], y)));
-  const V c2[3] = {Q::dup(g.centre[0]), Q::dup(g.centre[1]), Q::dup(g.centre[2])};
-  for (int i = 0; i < npd; ++i) {
-    const S3ZProd<T> e = sh.zp[i];
-    const V rx2 = Q::add(Q::add(sxy[0], Q::dup(e.p[0])), c2[0]);
-    const V ry2 = Q::add(Q::add(sxy[1], Q::dup(e.p[1])), c2[1]);
-    const V rz2 = Q::add(Q::add(sxy[2], Q::dup(e.p[2])), c2[2]);
-    const T rx[2] = {Q::lo(rx2), Q::hi(rx2)}, ry[2] = {Q::lo(ry2), Q::hi(ry2)}, rz[2] = {Q::lo(rz2), Q::hi(rz2)};
-    T w[2][8], v[2][8];
-    bool in[2];
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      long long off[8];
-      in[s] = make_taps<T, 3>(p.D, p.H, p.W, rz[s], ry[s], rx[s], p.order, w[s], off);
-      if (s == 1) in[s] = in[s] && has_b;
-      if (in[s]) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) v[s][k] = __ldg(vol + off[k]);
-      } else {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) { v[s][k] = A::fi(0); w[s][k] = A::fi(0); }
-      }
-    }
-    V acc = Q::tap_first(Q::make(w[0][0], w[1][0]), Q::make(v[0][0], v[1][0]),
-                         Q::make(w[0][1], w[1][1]), Q::make(v[0][1], v[1][1]));
-#pragma unroll
-    for (int k = 2; k < 8; ++k) acc = Q::tap_next(acc, Q::make(w[0][k], w[1][k]), Q::make(v[0][k], v[1][k]));
-    const V val = Q::select(Q::add(zero2, acc), in[0], in[1]);
-    T* o = out + i * plane_o;
-    if (vec) {
-      Q::store2(o, val);
-    } else {
-      o[0] = Q::lo(val);
-      if (has_b) o[1] = Q::hi(val);
-    }
-  }
+  // ---- general rotation: positions change with depth
+  s3_full_depth_loop<T, 1>(p, sh, npd, c, pw0, ph, kS3TileH, L.vec_store != 0, out);
 }
 
 template <typename T>

@@ -184,12 +184,24 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
   s3_prologue<T>(p, k, sh.s3);  // ends with __syncthreads()
   const RoiGeom<T>& g = sh.s3.g;
   const bool bad_batch = (g.batch < 0 || g.batch >= p.N);
-  if (!sh.s3.zsep || bad_batch) {  // CTA-uniform: plain loads, one 16-row sub-tile at a time
+  if (bad_batch) {  // CTA-uniform: zeros and the status bit, one 16-row sub-tile at a time
     if (threadIdx.x < kS3Threads) {
       for (int q = 0; q < NP; ++q) {
         S3Cta k2 = k;
         k2.th = k.th * NP + q;
         if (k2.th * kS3TileH < p.oh) s3_body_l1<T>(p, L, k2, sh.s3);
+      }
+    }
+    return;
+  }
+  if (!sh.s3.zsep) {  // CTA-uniform: general rotation, gathered with plain loads by the consumer warps
+    if (threadIdx.x < kS3Threads) {
+      const int lane_ = threadIdx.x & 31, warp_ = threadIdx.x >> 5;
+      const int pw = k.tw * kS3TileW + (warp_ & 1) * 16 + (lane_ & 7) * 2;
+      const int ph = k.th * (kS3TileH * NP) + (warp_ >> 1) * 4 + (lane_ >> 3);
+      if (pw < p.ow && ph < p.oh) {
+        T* out0 = (T*)p.out + k.nc * p.ovol + (long long)k.pd0 * p.oh * p.ow + (long long)ph * p.ow + pw;
+        s3_full_depth_loop<T, NP>(p, sh.s3, k.npd, k.c, pw, ph, kS3TileH, L.vec_store != 0, out0);
       }
     }
     return;
@@ -532,7 +544,8 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   if (dtype == 0 && p.fm != kS3FloatPattern) return MVR_STREAM3D_NOT_APPLICABLE;
   // small outputs (detection heads) are better served one element per thread
   if (p.ovol < 4096 || p.ow < 8) return MVR_STREAM3D_NOT_APPLICABLE;
-  if ((long long)p.H * p.W >= 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
+  if (p.vol >= 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;           // 32-bit offsets inside a volume
+  if (dtype == 1 && (p.D > 2048 || p.H > 2048 || p.W > 2048)) return MVR_STREAM3D_NOT_APPLICABLE;  // sizes as half values
 
   static const bool use_tma = getenv("MVR_NO_TMA") == nullptr;
   T3Maps maps;
