@@ -121,6 +121,11 @@ class Ours:
     def public_forward(self, feat, rois, out_size, order):
         return self.affine_3d(feat, rois, tuple(out_size), 1.0, 1, True, order)
 
+    def host_forward(self, feat_h, rois_h, out_size, order, out_h):
+        """host tensors in, host tensor out: the library's pipelined entry point"""
+        from medvision_b200.ops import affine_from_host
+        return affine_from_host(feat_h, rois_h, tuple(out_size), 1.0, 1, True, order, out=out_h)
+
 
 class ReferenceCuda:
     """The reference's own kernels (oracle/_ref), called like medvision/ops/cuda_fun_tools.py:48-91."""
@@ -156,7 +161,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -331,6 +336,9 @@ def measure_e2e(impl, wl, steps, warmup, world):
     out_h = torch.empty(out_shape, dtype=feat_h.dtype).pin_memory()
 
     def step():
+        if hasattr(impl, "host_forward"):
+            impl.host_forward(feat_h, rois_h, wl["out_size"], wl["order"], out_h)
+            return
         f = feat_h.cuda(non_blocking=True)
         r = rois_h.cuda(non_blocking=True)
         o = impl.public_forward(f, r, wl["out_size"], wl["order"])
@@ -359,12 +367,13 @@ def run_cpu_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5")
     ap.add_argument("--small", action="store_true", help="reduced copy of the workload (for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true", help="skip e2e, CPU baselines and the extra configurations")
+    ap.add_argument("--backward", action="store_true", help="time forward + backward instead of forward (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -384,7 +393,7 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms, out = measure(impl, wl, args.steps, args.warmup, world)
+    ms, out = measure(impl, wl, args.steps, args.warmup, world, backward=args.backward)
     clocks = sampler.stop() if rank == 0 else None
     value = world * n_out / (ms * 1e-3) / 1e9
 
@@ -413,7 +422,7 @@ def main():
                         "frac_of_8000_nominal": achieved / 8000.0}
 
     if not args.kernel_only:
-        ems, h2d, d2h, _ = measure_e2e(impl, wl, max(2, args.steps // 4), 3, world)
+        ems, h2d, d2h, _ = measure_e2e(impl, wl, max(2, min(args.steps // 4, 10)), 3, world)
         line["e2e"] = {"value": world * n_out / (ems * 1e-3) / 1e9, "unit": "Gvoxel/s", "ms_per_step": ems,
                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
         if args.impl == "reference" and rank == 0:
@@ -432,7 +441,7 @@ def main():
             for key, bwd in (("c3", False), ("c4", False), ("c4", True)):
                 w2 = WORKLOADS[key]("cuda", 0)
                 n2 = w2["rois"].size(0) * math.prod(w2["out_size"])
-                m2, _ = measure(impl, w2, max(args.steps, 20), args.warmup, 1, backward=bwd)
+                m2, _ = measure(impl, w2, min(max(args.steps, 20), 100), min(args.warmup, 10), 1, backward=bwd)
                 r2 = w2["rois"].to(w2["features"].dtype).cuda()
                 U2 = touched_elements(w2["features"], r2, w2["out_size"], 1)
                 b2 = 2 * (U2 + n2) + r2.numel() * 2

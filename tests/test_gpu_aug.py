@@ -84,3 +84,20 @@ def test_crop_with_affine_times_equals_replicated_batch():
     rois_rep[:, 0] = torch.arange(6)
     want = affine_3d(rep, rois_rep.cuda(), (8, 16, 16), 1.0, 1, True, 1)
     assert torch.equal(out["img"], want)
+
+
+def test_host_pipeline_equals_one_call():
+    from medvision_b200.ops import affine_3d, affine_from_host
+    g = torch.Generator().manual_seed(8)
+    vol = torch.rand(3, 2, 12, 24, 32, generator=g).half().pin_memory()
+    R = 9
+    b = torch.tensor([2, 0, 1, 1, 0, 2, 2, 0, 0]).float().view(-1, 1)  # unsorted batch indices
+    rois = torch.cat([b, torch.rand(R, 3, generator=g) * torch.tensor([32., 24., 12.]),
+                      torch.rand(R, 3, generator=g) * 10 + 4, torch.zeros(R, 2), torch.rand(R, 1, generator=g) - .5], 1)
+    got = affine_from_host(vol, rois, (6, 8, 8), 1.0, 1, True, 1)
+    want = affine_3d(vol.cuda(), rois.cuda(), (6, 8, 8), 1.0, 1, True, 1).cpu()
+    assert got.is_pinned() and torch.equal(got, want)
+    sorted_rois = rois[torch.argsort(rois[:, 0], stable=True)]
+    got2 = affine_from_host(vol, sorted_rois, (6, 8, 8), 1.0, 1, True, 0)
+    want2 = affine_3d(vol.cuda(), sorted_rois.cuda(), (6, 8, 8), 1.0, 1, True, 0).cpu()
+    assert torch.equal(got2, want2)
