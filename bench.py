@@ -101,6 +101,11 @@ def workload_c4(device, rank, small=False):
 
 WORKLOADS = {"c5": workload_c5, "c3": workload_c3, "c4": workload_c4}
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per output voxel of this library's
+# forward kernel, from one ncu capture of a reduced copy of the workload (profiles/); traffic grows
+# in proportion to the voxels processed, so a launch's traffic is this figure times its outputs.
+DRAM_BYTES_PER_OUTPUT_VOXEL = {"c5": 4.175, "c3": 10.6}
+
 
 # ----------------------------------------------------------------------------- implementations
 class Ours:
@@ -417,7 +422,9 @@ def main():
     peak, peak_src = load_peaks()
     achieved = alg_bytes / (ms * 1e-3) / 1e9
     line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                        "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
+                        "traffic": (DRAM_BYTES_PER_OUTPUT_VOXEL.get(args.workload) * n_out
+                                    if args.impl == "ours" and DRAM_BYTES_PER_OUTPUT_VOXEL.get(args.workload) else None),
+                        "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
                         "distinct_input_elements": U, "output_elements": n_out,
                         "frac_of_8000_nominal": achieved / 8000.0}
 

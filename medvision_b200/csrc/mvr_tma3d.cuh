@@ -22,7 +22,8 @@
 // abort flag that ends the other waits; the producer leaves only after its own copies in flight
 // have landed (bounded again).
 //
-// No cluster launch, no multicast: every CTA fetches its own boxes from this GPU's memory.
+// Every CTA fetches its own boxes from this GPU's memory; no copy is shared between CTAs and
+// there is no cluster launch.
 #pragma once
 #include <cuda.h>
 
