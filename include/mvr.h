@@ -180,13 +180,13 @@ int mvr_roi_align_rotated_3d_backward(const void* top_grad, const void* rois, vo
                                       int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned,
                                       int order, int* status, void* stream);
 /* medvision/csrc/vision.cpp:74  affine_2d(input, rois, output, oh, ow, spatial_scale, sampling_ratio, aligned, order)
- * (medvision/csrc/affine_2d.h) -- forward only */
+ * (medvision/csrc/affine_2d.h) -- forward only; order may also be 3 (Catmull-Rom) */
 int mvr_affine_2d(const void* input, const void* rois, void* output, int dtype,
                   int64_t N, int64_t C, int64_t H, int64_t W, int64_t R, int roi_width,
                   int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
                   int* status, void* stream);
 /* medvision/csrc/vision.cpp:75  affine_3d(input, rois, output, od, oh, ow, spatial_scale, sampling_ratio, aligned, order)
- * (medvision/csrc/affine_3d.h:40-65) -- forward only */
+ * (medvision/csrc/affine_3d.h:40-65) -- forward only; order may also be 3 (Catmull-Rom) */
 int mvr_affine_3d(const void* input, const void* rois, void* output, int dtype,
                   int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
                   int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,

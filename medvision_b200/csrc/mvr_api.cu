@@ -52,11 +52,12 @@ std::atomic<int> g_contraction(kReferenceContraction);
 int roi_width_of(int ndim, int kind) { return kind == KIND_BOX ? (ndim == 2 ? 5 : 7) : (ndim == 2 ? 6 : 10); }
 
 int check_common(const void* a, const void* rois, void* b, int dtype, int ndim, int kind, int64_t N, int64_t C,
-                 int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh, int ow, int order) {
+                 int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh, int ow, int order,
+                 bool allow_cubic = false) {
   if (dtype != MVR_F32 && dtype != MVR_F16 && dtype != MVR_F64) return MVR_ERR_DTYPE;
   if (ndim != 2 && ndim != 3) return MVR_ERR_NDIM;
   if (kind != MVR_ROI_BOX && kind != MVR_ROI_ROTATED) return MVR_ERR_ROI_KIND;
-  if (order != 0 && order != 1) return MVR_ERR_ORDER;
+  if (order != 0 && order != 1 && !(allow_cubic && order == 3)) return MVR_ERR_ORDER;
   if (roi_width != roi_width_of(ndim, kind)) return MVR_ERR_ROI_WIDTH;
   if (N < 0 || C < 0 || R < 0 || D < 1 || H < 1 || W < 1 || od < 1 || oh < 1 || ow < 1) return MVR_ERR_SHAPE;
   if (ndim == 2 && (D != 1 || od != 1)) return MVR_ERR_SHAPE;
@@ -149,15 +150,24 @@ int mvr_version(void) { return 1; }
 int mvr_set_float_contraction(int bits) { return g_contraction.exchange(bits & 0x00ffffff); }
 int mvr_get_float_contraction(void) { return g_contraction.load(); }
 
-int mvr_roi_resample_fwd(const void* features, const void* rois, void* output, int dtype, int ndim, int roi_kind,
-                         int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
-                         int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
-                         int* status, void* stream) {
-  int rc = check_common(features, rois, output, dtype, ndim, roi_kind, N, C, D, H, W, R, roi_width, od, oh, ow, order);
+static int resample_fwd_impl(const void* features, const void* rois, void* output, int dtype, int ndim, int roi_kind,
+                             int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od,
+                             int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                             int* status, void* stream, bool allow_cubic) {
+  int rc = check_common(features, rois, output, dtype, ndim, roi_kind, N, C, D, H, W, R, roi_width, od, oh, ow, order,
+                        allow_cubic);
   if (rc != MVR_OK) return rc;
   Params p = make_params(features, rois, output, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow, spatial_scale,
                          sampling_ratio, aligned, order, status);
   return dispatch(p, dtype, true, (cudaStream_t)stream);
+}
+
+int mvr_roi_resample_fwd(const void* features, const void* rois, void* output, int dtype, int ndim, int roi_kind,
+                         int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                         int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
+                         int* status, void* stream) {
+  return resample_fwd_impl(features, rois, output, dtype, ndim, roi_kind, N, C, D, H, W, R, roi_width, od, oh, ow,
+                           spatial_scale, sampling_ratio, aligned, order, status, stream, false);
 }
 
 int mvr_roi_resample_bwd(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim, int roi_kind,
@@ -276,14 +286,15 @@ int mvr_roi_align_rotated_3d_backward(const void* top_grad, const void* rois, vo
 int mvr_affine_2d(const void* input, const void* rois, void* output, int dtype, int64_t N, int64_t C, int64_t H,
                   int64_t W, int64_t R, int roi_width, int oh, int ow, float spatial_scale, int sampling_ratio,
                   int aligned, int order, int* status, void* stream) {
-  return mvr_roi_resample_fwd(input, rois, output, dtype, 2, MVR_ROI_ROTATED, N, C, 1, H, W, R, roi_width, 1, oh, ow,
-                              spatial_scale, sampling_ratio, aligned, order, status, stream);
+  // the only entry points with order 3 (Catmull-Rom), as in the reference
+  return resample_fwd_impl(input, rois, output, dtype, 2, MVR_ROI_ROTATED, N, C, 1, H, W, R, roi_width, 1, oh, ow,
+                           spatial_scale, sampling_ratio, aligned, order, status, stream, true);
 }
 int mvr_affine_3d(const void* input, const void* rois, void* output, int dtype, int64_t N, int64_t C, int64_t D,
                   int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh, int ow, float spatial_scale,
                   int sampling_ratio, int aligned, int order, int* status, void* stream) {
-  return mvr_roi_resample_fwd(input, rois, output, dtype, 3, MVR_ROI_ROTATED, N, C, D, H, W, R, roi_width, od, oh, ow,
-                              spatial_scale, sampling_ratio, aligned, order, status, stream);
+  return resample_fwd_impl(input, rois, output, dtype, 3, MVR_ROI_ROTATED, N, C, D, H, W, R, roi_width, od, oh, ow,
+                           spatial_scale, sampling_ratio, aligned, order, status, stream, true);
 }
 
 }  // extern "C"

@@ -118,7 +118,9 @@ resample_fwd_generic(const Params p) {
         T w[1 << NDIM], v[1 << NDIM];
         long long off[1 << NDIM];
         T val = A::fi(0);
-        if (make_taps<T, NDIM>(p.D, p.H, p.W, sz, sy, sx, p.order, w, off)) {
+        if (p.order == 3) {
+          val = (NDIM == 2) ? hermite_2d<T>(vol, p.H, p.W, sy, sx, p.fm) : hermite_3d<T>(vol, p.D, p.H, p.W, sz, sy, sx, p.fm);
+        } else if (make_taps<T, NDIM>(p.D, p.H, p.W, sz, sy, sx, p.order, w, off)) {
 #pragma unroll
           for (int k = 0; k < (1 << NDIM); ++k) v[k] = __ldg(vol + off[k]);
           val = tap_sum<T, (1 << NDIM)>(w, v, p.fm);

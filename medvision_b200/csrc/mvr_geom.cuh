@@ -284,4 +284,109 @@ __device__ __forceinline__ T tap_sum(const T* w, const T* v, int fm) {
   return acc;
 }
 
+// ---- Catmull-Rom (order 3) of the affine_* entry points --------------------------------------
+// medvision/csrc/cuda_aug/interpolation_helpers_2d.h:335-424, interpolation_helpers_3d.h:572-792.
+// Per axis: i1 = (int)c after the c <= 0 clamp, u = c - i1 (element type, then float), taps
+// i1-1 .. i1+2 clamped into the image.  The reference writes every one of the 16 / 64 weights as a
+// polynomial in DOUBLE over u, u^2, u^3 (u^2, u^3 rounded to float in 2D and to the element type
+// in 3D) and rounds the result to the element type; those polynomials are the products of the
+// per-axis cubics below, so the weights here are the products of three doubles -- equal to the
+// reference's up to ~1e-16 before the rounding to the element type.
+template <typename T>
+__device__ __forceinline__ T from_double(double d);
+template <> __device__ __forceinline__ float from_double<float>(double d) { return __double2float_rn(d); }
+template <> __device__ __forceinline__ double from_double<double>(double d) { return d; }
+template <> __device__ __forceinline__ __half from_double<__half>(double d) {
+  return __float2half_rn(__double2float_rn(d));  // c10::Half(double) goes through float
+}
+
+template <typename T, bool POWERS_IN_T>
+__device__ __forceinline__ void hermite_axis(T c, int size, int* idx, double* w) {
+  typedef Ar<T> A;
+  if (A::le_zero(c)) c = A::fi(0);
+  const int i1 = A::toi(c);
+  const float u = A::tof(A::sub(c, A::fi(i1)));
+  double u2, u3;
+  if (POWERS_IN_T) {  // 3D: `T ux2 = ux * ux; T ux3 = ux * ux * ux;` with float ux
+    u2 = (double)A::tof(A::ff(__fmul_rn(u, u)));
+    u3 = (double)A::tof(A::ff(__fmul_rn(__fmul_rn(u, u), u)));
+  } else {            // 2D: float ux2, ux3
+    u2 = (double)__fmul_rn(u, u);
+    u3 = (double)__fmul_rn(__fmul_rn(u, u), u);
+  }
+  const double ud = (double)u;
+  w[0] = -0.5 * u3 + u2 - 0.5 * ud;
+  w[1] = 1.5 * u3 - 2.5 * u2 + 1.0;
+  w[2] = -1.5 * u3 + 2.0 * u2 + 0.5 * ud;
+  w[3] = 0.5 * u3 - 0.5 * u2;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) idx[k] = min(max(i1 - 1 + k, 0), size - 1);
+}
+
+// running sum of w*v in the reference's order; float fuses as in the linear tap sum
+template <typename T>
+__device__ __forceinline__ T hermite_group4(const T* w, const T* v, int fm) {
+  typedef Ar<T> A;
+  if (A::kCanFuse && Fm::tap(fm)) {
+    T t = A::fma_(w[0], v[0], A::mul(w[1], v[1]));
+    t = A::fma_(w[2], v[2], t);
+    return A::fma_(w[3], v[3], t);
+  }
+  T t = A::add(A::mul(w[0], v[0]), A::mul(w[1], v[1]));
+  t = A::add(t, A::mul(w[2], v[2]));
+  return A::add(t, A::mul(w[3], v[3]));
+}
+
+template <typename T>
+__device__ T hermite_2d(const T* __restrict__ img, int H, int W, T y, T x, int fm) {
+  typedef Ar<T> A;
+  if (axis_outside<T>(y, H) || axis_outside<T>(x, W)) return A::fi(0);
+  int ix[4], iy[4];
+  double wx[4], wy[4];
+  hermite_axis<T, false>(x, W, ix, wx);
+  hermite_axis<T, false>(y, H, iy, wy);
+  // one 16-term expression, summed left to right: w00*v00 + w10*v10 + ... (x fastest)
+  T acc = A::fi(0);
+  bool first = true;
+  T pw = A::fi(0), pv = A::fi(0);
+  for (int j = 0; j < 4; ++j)
+    for (int i = 0; i < 4; ++i) {
+      const T w = from_double<T>(wx[i] * wy[j]);
+      const T v = __ldg(img + (long long)iy[j] * W + ix[i]);
+      if (j == 0 && i == 0) { pw = w; pv = v; continue; }
+      if (first) {
+        acc = (A::kCanFuse && Fm::tap(fm)) ? A::fma_(pw, pv, A::mul(w, v)) : A::add(A::mul(pw, pv), A::mul(w, v));
+        first = false;
+      } else {
+        acc = (A::kCanFuse && Fm::tap(fm)) ? A::fma_(w, v, acc) : A::add(acc, A::mul(w, v));
+      }
+    }
+  return acc;
+}
+
+template <typename T>
+__device__ T hermite_3d(const T* __restrict__ vol, int D, int H, int W, T z, T y, T x, int fm) {
+  typedef Ar<T> A;
+  if (axis_outside<T>(y, H) || axis_outside<T>(x, W) || axis_outside<T>(z, D)) return A::fi(0);
+  int ix[4], iy[4], iz[4];
+  double wx[4], wy[4], wz[4];
+  hermite_axis<T, true>(x, W, ix, wx);
+  hermite_axis<T, true>(y, H, iy, wy);
+  hermite_axis<T, true>(z, D, iz, wz);
+  // val = 0; val += (four terms along x) for every (y, z), z outermost
+  T val = A::fi(0);
+  for (int k = 0; k < 4; ++k)
+    for (int j = 0; j < 4; ++j) {
+      T w[4], v[4];
+      const T* row = vol + ((long long)iz[k] * H + iy[j]) * W;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w[i] = from_double<T>(wx[i] * wy[j] * wz[k]);
+        v[i] = __ldg(row + ix[i]);
+      }
+      val = A::add(val, hermite_group4<T>(w, v, fm));
+    }
+  return val;
+}
+
 }  // namespace mvr

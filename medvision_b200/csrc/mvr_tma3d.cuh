@@ -540,7 +540,7 @@ inline size_t t3_dynamic_smem(int ring_bytes) { return (size_t)ring_bytes + size
 // Picks the streaming kernel when the call has its shape; returns MVR_STREAM3D_NOT_APPLICABLE
 // otherwise (the caller then uses the general kernel).
 inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
-  if (p.ndim != 3 || p.sampling_ratio != 1) return MVR_STREAM3D_NOT_APPLICABLE;
+  if (p.ndim != 3 || p.sampling_ratio != 1 || p.order > 1) return MVR_STREAM3D_NOT_APPLICABLE;
   if (dtype != 0 /*f32*/ && dtype != 1 /*f16*/) return MVR_STREAM3D_NOT_APPLICABLE;
   if (dtype == 0 && p.fm != kS3FloatPattern) return MVR_STREAM3D_NOT_APPLICABLE;
   // small outputs (detection heads) are better served one element per thread

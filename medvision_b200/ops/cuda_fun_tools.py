@@ -7,8 +7,6 @@ import torch
 from .. import _C
 from ._common import parse_output_size
 
-# order 3 (Catmull-Rom) of the reference's affine kernels is not part of this library yet
-_SUPPORTED_ORDERS = [0, 1]
 
 
 def _affine(ndim, features, rois, out_size, spatial_scale, sampling_ratio, aligned, order):
@@ -16,8 +14,6 @@ def _affine(ndim, features, rois, out_size, spatial_scale, sampling_ratio, align
     assert features.dtype in [torch.float32, torch.float16], \
         f'input must be float16 or float32 but got {features.dtype}'
     assert order in [0, 1, 3], f'order {order} is not supported!'
-    if order not in _SUPPORTED_ORDERS:
-        raise NotImplementedError(f"order {order} is not implemented by medvision_b200 (orders {_SUPPORTED_ORDERS} are)")
     if order == 0:
         # one sample per output voxel: averaging would blend labels
         sampling_ratio = 1

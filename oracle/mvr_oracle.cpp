@@ -441,10 +441,10 @@ inline typename A::T rot_row2(typename A::T x, typename A::T a, typename A::T y,
 // medvision/csrc/cuda_aug/interpolation_helpers_{2d,3d}.h hermite_*_interpolate.  Filled in by
 // hermite.inc-style code below (kept in this file).
 template <class A>
-typename A::T hermite_2d(const void* vol, int64_t base, int H, int W, typename A::T y, typename A::T x);
+typename A::T hermite_2d(const void* vol, int64_t base, int H, int W, typename A::T y, typename A::T x, int fma_mode);
 template <class A>
 typename A::T hermite_3d(const void* vol, int64_t base, int D, int H, int W, typename A::T z, typename A::T y,
-                         typename A::T x);
+                         typename A::T x, int fma_mode);
 
 // ------------------------------------------------------------------ drivers
 struct Args {
@@ -507,8 +507,8 @@ int run_fwd(const Args& a) {
                   }
                   T val = (T)0;
                   if (a.order == 3) {
-                    val = (a.ndim == 2) ? hermite_2d<A>(a.in, base, (int)a.H, (int)a.W, sy, sx)
-                                        : hermite_3d<A>(a.in, base, (int)a.D, (int)a.H, (int)a.W, sz, sy, sx);
+                    val = (a.ndim == 2) ? hermite_2d<A>(a.in, base, (int)a.H, (int)a.W, sy, sx, a.fma_mode)
+                                        : hermite_3d<A>(a.in, base, (int)a.D, (int)a.H, (int)a.W, sz, sy, sx, a.fma_mode);
                   } else {
                     T w[8], v[8];
                     int64_t off[8];
@@ -608,33 +608,83 @@ int run_bwd(const Args& a) {
 }
 
 // ------------------------------------------------------------------ Catmull-Rom bodies
-// The reference clamps each of the 4 tap indices into the image, forms the four cubic
-// weights per axis from u = c - floor(c) in `float`, multiplies them out and sums.
-// (Restated once order 3 is wired up in the library; see hermite_weights.)
+// medvision/csrc/cuda_aug/interpolation_helpers_2d.h:335-424, interpolation_helpers_3d.h:572-792.
+// Per axis: i1 = (int)c after the c <= 0 clamp; u = c - i1 in the element type, held as float;
+// u^2 and u^3 are float products (2D: kept as float; 3D: rounded to the element type); the
+// reference then evaluates each of the 16 / 64 weights as an expanded polynomial in DOUBLE and
+// rounds it to the element type.  Those polynomials factor exactly into the per-axis cubics
+// below, so the weights are formed here as products of doubles: the same real numbers, equal in
+// double up to ~1e-16 before the final rounding.
 template <class A>
-inline void hermite_weights(float u, float* w) {
-  // a = -0.5 Catmull-Rom: w0=-.5u^3+u^2-.5u, w1=1.5u^3-2.5u^2+1, w2=-1.5u^3+2u^2+.5u, w3=.5u^3-.5u^2
-  const float u2 = u * u, u3 = u2 * u;
-  w[0] = -0.5f * u3 + u2 - 0.5f * u;
-  w[1] = 1.5f * u3 - 2.5f * u2 + 1.0f;
-  w[2] = -1.5f * u3 + 2.0f * u2 + 0.5f * u;
-  w[3] = 0.5f * u3 - 0.5f * u2;
+inline typename A::T from_double(double d) { return A::fd(d); }
+
+template <class A, bool POWERS_IN_T>
+inline void hermite_axis(typename A::T c, int size, int* idx, double* w) {
+  typedef typename A::T T;
+  if (c <= (T)0) c = (T)0;
+  const int i1 = (c == c) ? (int)c : 0;
+  const float u = (float)A::sub(c, A::fi(i1));
+  double u2, u3;
+  if (POWERS_IN_T) {
+    u2 = (double)A::ff(u * u);
+    u3 = (double)A::ff((u * u) * u);
+  } else {
+    u2 = (double)(float)(u * u);
+    u3 = (double)(float)((float)(u * u) * u);
+  }
+  const double ud = (double)u;
+  w[0] = -0.5 * u3 + u2 - 0.5 * ud;
+  w[1] = 1.5 * u3 - 2.5 * u2 + 1.0;
+  w[2] = -1.5 * u3 + 2.0 * u2 + 0.5 * ud;
+  w[3] = 0.5 * u3 - 0.5 * u2;
+  for (int k = 0; k < 4; ++k) idx[k] = std::min(std::max(i1 - 1 + k, 0), size - 1);
 }
 
 template <class A>
-typename A::T hermite_2d(const void*, int64_t, int, int, typename A::T, typename A::T) {
-  return (typename A::T)NAN;  // order 3 is not restated yet; callers reject it before this point
-}
-template <class A>
-typename A::T hermite_3d(const void*, int64_t, int, int, int, typename A::T, typename A::T, typename A::T) {
-  return (typename A::T)NAN;
+typename A::T hermite_2d(const void* vol, int64_t base, int H, int W, typename A::T y, typename A::T x, int fma_mode) {
+  typedef typename A::T T;
+  if (outside<A>(y, H) || outside<A>(x, W)) return (T)0;
+  int ix[4], iy[4];
+  double wx[4], wy[4];
+  hermite_axis<A, false>(x, W, ix, wx);
+  hermite_axis<A, false>(y, H, iy, wy);
+  T w[16], v[16];
+  for (int j = 0; j < 4; ++j)
+    for (int i = 0; i < 4; ++i) {
+      w[j * 4 + i] = from_double<A>(wx[i] * wy[j]);
+      v[j * 4 + i] = A::ld(vol, base + (int64_t)iy[j] * W + ix[i]);
+    }
+  return tap_sum<A>(w, v, 16, fma_mode);  // one left-to-right sum, x fastest
 }
 
-int check(const Args& a, int dtype) {
+template <class A>
+typename A::T hermite_3d(const void* vol, int64_t base, int D, int H, int W, typename A::T z, typename A::T y,
+                         typename A::T x, int fma_mode) {
+  typedef typename A::T T;
+  if (outside<A>(y, H) || outside<A>(x, W) || outside<A>(z, D)) return (T)0;
+  int ix[4], iy[4], iz[4];
+  double wx[4], wy[4], wz[4];
+  hermite_axis<A, true>(x, W, ix, wx);
+  hermite_axis<A, true>(y, H, iy, wy);
+  hermite_axis<A, true>(z, D, iz, wz);
+  T val = (T)0;  // val = 0; val += (four terms along x), for every (y, z), z outermost
+  for (int k = 0; k < 4; ++k)
+    for (int j = 0; j < 4; ++j) {
+      T w[4], v[4];
+      for (int i = 0; i < 4; ++i) {
+        w[i] = from_double<A>(wx[i] * wy[j] * wz[k]);
+        v[i] = A::ld(vol, base + ((int64_t)iz[k] * H + iy[j]) * W + ix[i]);
+      }
+      val = A::add(val, tap_sum<A>(w, v, 4, fma_mode));
+    }
+  return val;
+}
+
+int check(const Args& a, int dtype, bool fwd) {
   if (dtype != DT_F32 && dtype != DT_F16 && dtype != DT_F64) return -1;
   if (a.ndim != 2 && a.ndim != 3) return -2;
   if (a.kind != KIND_BOX && a.kind != KIND_ROTATED) return -3;
-  if (a.order != 0 && a.order != 1) return -4;
+  if (a.order != 0 && a.order != 1 && !(fwd && a.order == 3 && a.kind == KIND_ROTATED)) return -4;
   if (a.ndim == 2 && (a.D != 1 || a.od != 1)) return -5;
   if (a.N < 0 || a.C < 0 || a.D < 1 || a.H < 1 || a.W < 1 || a.R < 0 || a.od < 1 || a.oh < 1 || a.ow < 1) return -6;
   return 0;
@@ -653,7 +703,7 @@ int mvr_oracle_fwd(const void* features, const void* rois, void* output, int dty
                    const void* trig) {
   Args a = {features, rois, output, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow,
             spatial_scale, sampling_ratio, aligned, order, fma_mode, 0, nthreads, trig};
-  int e = check(a, dtype);
+  int e = check(a, dtype, true);
   if (e) return e;
   switch (dtype) {
     case DT_F32: return run_fwd<Arith<DT_F32> >(a);
@@ -671,7 +721,7 @@ int mvr_oracle_bwd(const void* grad_out, const void* rois, void* grad_in, int dt
                    int nthreads, const void* trig) {
   Args a = {grad_out, rois, grad_in, ndim, roi_kind, N, C, D, H, W, R, od, oh, ow,
             spatial_scale, sampling_ratio, aligned, order, fma_mode, wide_acc, nthreads, trig};
-  int e = check(a, dtype);
+  int e = check(a, dtype, false);
   if (e) return e;
   switch (dtype) {
     case DT_F32: return run_bwd<Arith<DT_F32> >(a);

@@ -52,6 +52,17 @@ def all_cases():
                                                aligned=aligned, spatial=spatial, out_size=out_size, seed=seed,
                                                N=2, C=3, R=7,
                                                spatial_scale={(1, 2): 1.0, (1, 0): 0.5, (0, 1): 0.77, (1, 1): 0.3}[(order, sr)])))
+    # Catmull-Rom (order 3) exists in the forward-only affine_2d / affine_3d entry points
+    for ndim in (2, 3):
+        spatial = (20, 24) if ndim == 2 else (9, 12, 14)
+        out_size = (7, 6) if ndim == 2 else (4, 5, 6)
+        for dtype in (torch.float32, torch.float16):
+            for sr in (1, 2):
+                seed += 1
+                name = "%dd_affine_%s_o3_s%d" % (ndim, "f32" if dtype == torch.float32 else "f16", sr)
+                out.append((name, dict(ndim=ndim, kind=KIND_ROTATED, dtype=dtype, order=3, sampling_ratio=sr,
+                                       aligned=True, spatial=spatial, out_size=out_size, seed=seed, N=2, C=3, R=7,
+                                       spatial_scale=1.0, affine_only=True)))
     return out
 
 

@@ -35,6 +35,9 @@ def main():
         f, r, g = feat.cuda(), rois.cuda(), grad.cuda()
         kw = dict(spatial_scale=case["spatial_scale"], sampling_ratio=case["sampling_ratio"],
                   aligned=case["aligned"], order=case["order"])
+        if case.get("affine_only"):
+            blobs[name + "/fwd"] = to_np(ref.forward(f, r, case["out_size"], case["kind"], affine=True, **kw))
+            continue
         fwd = ref.forward(f, r, case["out_size"], case["kind"], **kw)
         bwd = ref.backward(g, r, feat.shape, case["kind"], **kw)
         blobs[name + "/fwd"] = to_np(fwd)

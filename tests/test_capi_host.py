@@ -91,6 +91,8 @@ def test_output_size_conventions():
         RoIAlignRotated((2, 2, 2, 2), 1.0)
     with pytest.raises(AssertionError, match="only support order"):
         RoIAlign((2, 2), 1.0)(torch.zeros(1, 1, 4, 4), torch.zeros(1, 5), order=3)
+    with pytest.raises(RuntimeError, match="not implemented on CPU"):
+        affine_3d(torch.zeros(1, 1, 4, 4, 4), torch.zeros(1, 10), 2, 1.0, order=3)  # order 3 is accepted
     with pytest.raises(AssertionError, match="not supported"):
         affine_3d(torch.zeros(1, 1, 4, 4, 4), torch.zeros(1, 10), 2, 1.0, order=2)
     with pytest.raises(AssertionError, match="float16 or float32"):

@@ -15,7 +15,9 @@ pytestmark = pytest.mark.gpu
 
 REF_FM = 1 | (1 << 1) | (1 << 2) | (1 << 3) | (1 << 5) | (1 << 7) | (1 << 10) | (1 << 13) | \
     (1 << 16) | (1 << 18) | (2 << 20) | (1 << 22)
-CASES = cases.all_cases()
+ALL = cases.all_cases()
+CASES = [(n, c) for n, c in ALL if not c.get("affine_only")]
+CUBIC = [(n, c) for n, c in ALL if c.get("affine_only")]
 GOLD = load_golden()
 
 
@@ -87,6 +89,21 @@ def test_affine_entry_equals_rotated_entry(name, case):
     a = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], affine=True, **_kw(case))
     b = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], **_kw(case))
     assert n_mismatch(a, b) == 0
+
+
+@pytest.mark.parametrize("name,case", CUBIC, ids=[n for n, _ in CUBIC])
+def test_catmull_rom_affine(name, case):
+    feat, rois, _ = cases.make_inputs(case)
+    out = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], affine=True, **_kw(case))
+    gold = golden_tensor(GOLD, name + "/fwd", case["dtype"])
+    assert_close(out, gold, FWD_TOL[case["dtype"]], name + " vs reference kernels")
+    oracle = port.forward(feat, rois, case["out_size"], case["kind"], trig=port.device_trig(rois),
+                          fma_mode=REF_FM if case["dtype"] == torch.float32 else 0, **_kw(case))
+    assert_close(out, oracle, FWD_TOL[case["dtype"]], name + " vs restatement")
+    # RoIAlign / RoIAlignRotated do not take order 3
+    from medvision_b200 import _C
+    with pytest.raises(RuntimeError, match="only support order"):
+        lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], affine=False, **_kw(case))
 
 
 # ------------------------------------------------------------------ streaming 3D kernel
