@@ -103,3 +103,19 @@ def test_crop_times_share_the_images():
     assert np.all(t.params["start"] == np.array([3, 2, 2]))
     with pytest.raises(AssertionError):
         BatchCudaCropRandomWithAffine(patch_size=(40, 6, 6), scale=0, shift=0, rotate=0)._forward_params(_result())
+
+
+def test_sliding_window_anchors():
+    from medvision_b200.aug_cuda import CudaPatches
+    t = CudaPatches(patch_size=(8, 8, 8), overlap=0.5)
+    res = {"img_dim": 3, "img": torch.zeros(1, 16, 20, 24)}
+    t._forward_params(res)
+    # stride 4; grid counts max((s-1)//4, 1) = 3, 4, 5 along z, y, x; x fastest; boxes in xyz order
+    assert t.params.shape == (60, 6)
+    assert t.params[0].tolist() == [0, 0, 0, 8, 8, 8] and t.params[1].tolist() == [4, 0, 0, 12, 8, 8]
+    assert t.params[-1].tolist() == [16, 12, 8, 24, 20, 16]
+    rois = t._rois()
+    assert rois[1].tolist() == [0, 8, 4, 4, 8, 8, 8, 0, 0, 0]
+    t2 = CudaPatches(patch_size=(6, 6), overlap=0.0)
+    t2._forward_params({"img_dim": 2, "img": torch.zeros(3, 5, 13)})
+    assert t2.params.tolist() == [[0, 0, 6, 6], [6, 0, 12, 6]]

@@ -101,3 +101,18 @@ def test_host_pipeline_equals_one_call():
     got2 = affine_from_host(vol, sorted_rois, (6, 8, 8), 1.0, 1, True, 0)
     want2 = affine_3d(vol.cuda(), sorted_rois.cuda(), (6, 8, 8), 1.0, 1, True, 0).cpu()
     assert torch.equal(got2, want2)
+
+
+def test_sliding_window_patches_are_the_slices():
+    from medvision_b200.aug_cuda import CudaPatches
+    g = torch.Generator().manual_seed(9)
+    img = torch.rand(2, 16, 24, 32, generator=g).half().cuda()
+    seg = torch.randint(0, 4, (1, 16, 24, 32), generator=g, dtype=torch.int32).cuda()
+    res = {"img_dim": 3, "img": img, "gt_seg": seg, "img_fields": ["img"], "seg_fields": ["gt_seg"]}
+    t = CudaPatches(patch_size=(8, 8, 16), overlap=0.5)
+    res = t(res)
+    patches, seg_patches = res["patches_img"], res["patches_gt_seg"]
+    assert patches.shape == (len(t.params), 2, 8, 8, 16) and seg_patches.dtype == torch.int32
+    for k, (x0, y0, z0, x1, y1, z1) in enumerate(t.params.tolist()):
+        assert torch.equal(patches[k], img[:, z0:z1, y0:y1, x0:x1])
+        assert torch.equal(seg_patches[k], seg[:, z0:z1, y0:y1, x0:x1])
