@@ -175,7 +175,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def window(self, t0, t1):
+        """keep only the samples that arrived inside [t0, t1] (the timed region)"""
+        self.t0, self.t1 = t0, t1
 
     def stop(self):
         if self.proc is None:
@@ -186,7 +190,11 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        t0, t1 = getattr(self, "t0", 0.0), getattr(self, "t1", float("inf"))
+        inside = [ln for ts, ln in self.lines if t0 <= ts <= t1 + 0.05]
+        if not inside:  # region shorter than one sampling period: take the nearest samples
+            inside = [ln for ts, ln in self.lines][-3:]
+        for ln in inside:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -272,24 +280,81 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
-def cpu_baseline_port(wl, budget_s=12.0):
-    """The CPU restatement of the reference kernels on the host cores, on a bounded sample of
-    the same workload: the first rois of the first volume."""
+def cpu_baseline_port(wl, budget_s=15.0):
+    """The CPU restatement of the reference kernels on all host cores, on a bounded sample of the
+    same workload: the rois of the first volumes, as many as fit the time budget."""
     from oracle import port
-    feat = wl["features"][:1].cpu()
-    rois = wl["rois"][wl["rois"][:, 0] == 0].to(feat.dtype).cpu()
+    rois_all = wl["rois"]
     threads = port.max_threads()
-    n = min(2, rois.size(0))
+    feat0 = wl["features"][:1].cpu()
+    probe = rois_all[rois_all[:, 0] == 0][:4].to(feat0.dtype).cpu()
     t0 = time.perf_counter()
-    port.forward(feat, rois[:n], wl["out_size"], port.KIND_ROTATED, 1.0, 1, True, wl["order"])
-    dt = time.perf_counter() - t0
-    per_roi = dt / n
-    n2 = int(max(n, min(rois.size(0), budget_s / max(per_roi, 1e-6))))
+    port.forward(feat0, probe, wl["out_size"], port.KIND_ROTATED, 1.0, 1, True, wl["order"])
+    per_roi = (time.perf_counter() - t0) / max(1, probe.size(0))
+    per_vol = int((rois_all[:, 0] == 0).sum())
+    n_vol = int(max(1, min(wl["features"].size(0), budget_s / max(per_roi * per_vol, 1e-6))))
+    feat = wl["features"][:n_vol].cpu()
+    rois = rois_all[rois_all[:, 0] < n_vol].to(feat.dtype).cpu()
     t0 = time.perf_counter()
-    out = port.forward(feat, rois[:n2], wl["out_size"], port.KIND_ROTATED, 1.0, 1, True, wl["order"])
+    out = port.forward(feat, rois, wl["out_size"], port.KIND_ROTATED, 1.0, 1, True, wl["order"])
     dt = time.perf_counter() - t0
     return {"value": out.numel() / dt / 1e9, "unit": "Gvoxel/s", "cores": threads, "kind": "port",
-            "sample": "%d of %d rois of volume 0, %.1f s" % (n2, wl["rois"].size(0), dt)}
+            "sample": "%d of %d rois (volumes 0..%d), %.1f s" % (rois.size(0), rois_all.size(0), n_vol - 1, dt)}
+
+
+def cpu_baseline_torch_function():
+    """The reference's torch-function RoIAlign path on CPU (restated in oracle/torch_function_path.py)
+    on BASELINE config 1: features (2,4,64,64,64) fp32, 128 rois, output 7^3, forward + backward."""
+    from oracle.torch_function_path import config1_inputs, roi_align_torch_function
+    feat, rois = config1_inputs()
+    feat.requires_grad_(True)
+    g = torch.Generator().manual_seed(2)
+    t0 = time.perf_counter()
+    out = roi_align_torch_function(feat, rois, (7, 7, 7), 1.0, 1)
+    t1 = time.perf_counter()
+    out.backward(torch.randn(out.shape, generator=g))
+    t2 = time.perf_counter()
+    return {"unit": "Gvoxel/s", "cores": torch.get_num_threads(), "kind": "port of medvision/ops/pytorch_ops/roi_align.py",
+            "sample": "config 1, 128 rois, whole", "fwd": out.numel() / (t1 - t0) / 1e9,
+            "fwd_bwd": out.numel() / (t2 - t0) / 1e9, "fwd_ms": (t1 - t0) * 1e3, "bwd_ms": (t2 - t1) * 1e3}
+
+
+def detection_configs(impl_name):
+    """Latency of the small detection-style configurations (BASELINE configs 1 and 2): forward and
+    forward + backward through the op modules, CUDA events over 200 calls each."""
+    if impl_name != "ours":
+        return None
+    from medvision_b200.ops import RoIAlign, RoIAlignRotated
+    from oracle.torch_function_path import config1_inputs
+    res = []
+
+    def run(name, module, feat, rois, n_out):
+        feat = feat.cuda().requires_grad_(True)
+        rois = rois.cuda().to(feat.dtype)
+        out = module(feat, rois)
+        grad = torch.randn_like(out)
+        for bwd in (False, True):
+            def step():
+                o = module(feat, rois)
+                if bwd:
+                    feat.grad = None
+                    o.backward(grad)
+            ms = time_steps(step, 200, 20, 1) / 200
+            res.append({"workload": name, "pass": "fwd+bwd" if bwd else "fwd", "us_per_call": ms * 1e3,
+                        "gvoxel_per_s": n_out / (ms * 1e-3) / 1e9, "note": "latency-bound; includes autograd and Python"})
+
+    feat, rois = config1_inputs()
+    run("RoIAlign 3D fp32 (2,4,64,64,64), 128 rois, 7x7x7, sampling_ratio 2",
+        RoIAlign((7, 7, 7), 1.0, 2), feat, rois, 128 * 4 * 343)
+    g = torch.Generator().manual_seed(2)
+    for dt in (torch.float32, torch.float16):
+        f2 = torch.randn(8, 3, 512, 512, generator=g).to(dt)
+        b = torch.randint(0, 8, (512, 1), generator=g).float()
+        r2 = torch.cat([b, torch.rand(512, 2, generator=g) * 512, torch.rand(512, 2, generator=g) * 240 + 16,
+                        (torch.rand(512, 1, generator=g) * 2 - 1) * math.pi], 1)
+        run("RoIAlignRotated 2D %s (8,3,512,512), 512 rois, 14x14, sampling_ratio 2" % str(dt)[6:],
+            RoIAlignRotated((14, 14), 1.0, 2), f2, r2, 512 * 3 * 196)
+    return res
 
 
 def cpu_baseline_scipy():
@@ -392,13 +457,15 @@ def main():
 
     rank, world, local = dist_setup(args.gpus)
     impl = Ours() if args.impl == "ours" else ReferenceCuda()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # started early: the tool needs a moment before its first sample
     wl = WORKLOADS[args.workload]("cuda", rank, small=args.small)
     n_out = wl["rois"].size(0) * wl["features"].size(1) * math.prod(wl["out_size"])
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    t_begin = time.time()
     ms, out = measure(impl, wl, args.steps, args.warmup, world, backward=args.backward)
+    sampler.window(t_begin, time.time())
     clocks = sampler.stop() if rank == 0 else None
     value = world * n_out / (ms * 1e-3) / 1e9
 
@@ -440,6 +507,7 @@ def main():
             sp = cpu_baseline_scipy()
             if sp:
                 line["cpu_baseline_aug_cpu"] = sp
+            line["cpu_baseline_torch_function"] = cpu_baseline_torch_function()
         if world == 1 and args.workload == "c5" and not args.small:
             extra = []
             del out
@@ -458,6 +526,9 @@ def main():
                               "gvoxel_per_s": n2 / (m2 * 1e-3) / 1e9, "algorithmic_bytes": b2,
                               "achieved_gbs": b2 / (m2 * 1e-3) / 1e9, "frac_of_peak": b2 / (m2 * 1e-3) / 1e9 / peak,
                               "note": "input fits in L2" if key == "c4" else "input larger than L2"})
+            det = detection_configs(args.impl)
+            if det:
+                extra += det
             line["other_configs"] = extra
     if rank == 0:
         print(json.dumps(line))

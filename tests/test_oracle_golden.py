@@ -157,3 +157,21 @@ def test_empty_roi_list():
     feat = torch.rand(1, 2, 4, 4)
     out = port.forward(feat, torch.zeros(0, 5), (2, 2), port.KIND_BOX)
     assert out.shape == (0, 2, 2, 2)
+
+
+def test_torch_function_baseline_restatement_matches_the_reference_module():
+    """The CPU timing baseline 'torch-function RoIAlign' is a restatement too; its pin is an output
+    of the reference's own module (tests/golden/make_torch_function_golden.py)."""
+    import numpy as np
+    import os
+    from oracle.torch_function_path import config1_inputs, roi_align_torch_function
+    from util import HERE
+    z = np.load(os.path.join(HERE, "golden", "torch_function_c1.npz"))
+    feat, rois = config1_inputs(n_rois=16)
+    feat.requires_grad_(True)
+    out = roi_align_torch_function(feat, rois, (7, 7, 7), 1.0, 1)
+    assert torch.equal(out.detach(), torch.from_numpy(z["out"]))
+    g = torch.Generator().manual_seed(2)
+    out.backward(torch.randn(out.shape, generator=g))
+    assert torch.allclose(feat.grad.sum(dim=(2, 3, 4)), torch.from_numpy(z["grad_sum"]), rtol=1e-5, atol=1e-5)
+    assert torch.allclose(feat.grad[0, 0, 30:34], torch.from_numpy(z["grad_slab"]), rtol=1e-5, atol=1e-6)
