@@ -1,4 +1,5 @@
-"""The ten resampling functions of the reference's compiled extension, on torch tensors.
+"""The resampling functions of the reference's compiled extension, on torch tensors: the ten
+roi / affine functions and ``deform_2d`` / ``deform_3d`` in the configuration ``apply_offset_*`` uses.
 
 Same names, argument order and error behaviour as ``medvision._C``
 (medvision/csrc/vision.cpp:34-48,74-75 and the dispatch headers medvision/csrc/roi_align_*.h,
@@ -151,3 +152,49 @@ def affine_3d(input, rois, output, aligned_depth, aligned_height, aligned_width,
               aligned, order):
     _run("affine_3d", "RoIAlignRotated", 3, 10, input, rois, output,
          (aligned_depth, aligned_height, aligned_width), spatial_scale, sampling_ratio, aligned, order, True)
+
+
+def _deform(name, ndim, input, weight, bias, offset, geometry, group, deformable_groups, order):
+    """The reference's ``deform_2d`` / ``deform_3d`` (medvision/csrc/vision.cpp:76-77) for the one
+    configuration its Python layer uses (medvision/ops/cuda_fun_tools.py:94-167): 1x1(x1) kernel,
+    stride 1, no padding, dilation 1, one group, one deformable group, identity weight and zero
+    bias -- i.e. a displacement-field warp.  ``weight`` and ``bias`` are accepted for signature
+    compatibility; anything but that configuration is refused."""
+    kernel, stride, padding, dilation = geometry
+    if not (all(k == 1 for k in kernel) and all(v == 1 for v in stride) and all(v == 0 for v in padding)
+            and all(v == 1 for v in dilation) and group == 1 and deformable_groups == 1):
+        raise NotImplementedError(f"{name}: only the 1x1 identity configuration of apply_offset_* is provided")
+    if not input.is_cuda:
+        raise RuntimeError("Not implemented on the CPU")
+    if tuple(weight.shape) != (input.size(1), input.size(1)) + (1,) * ndim:
+        raise NotImplementedError(f"{name}: the weight must be the channel identity")
+    if input.dim() != ndim + 2 or offset.dim() != ndim + 2 or offset.size(1) != ndim or \
+            offset.shape[2:] != input.shape[2:] or offset.size(0) != input.size(0):
+        raise RuntimeError(f"{name}: offset must be (B, {ndim}, *spatial) for input (B, C, *spatial)")
+    if offset.dtype != input.dtype or offset.device != input.device:
+        raise RuntimeError(f"expected scalar type {input.dtype} but found {offset.dtype}")
+    if input.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError(f'"{name}" not implemented for \'{str(input.dtype).replace("torch.", "")}\'')
+    assert input.is_contiguous(), "input tensor has to be contiguous"
+    offset = offset.contiguous()
+    out = torch.empty_like(input)
+    fn = getattr(_lib.lib, "mvr_apply_offset_%dd" % ndim)
+    with torch.cuda.device(input.device):
+        stream = torch.cuda.current_stream(input.device).cuda_stream
+        _call(fn, input.data_ptr(), offset.data_ptr(), out.data_ptr(), _DTYPES[input.dtype], input.size(0),
+              input.size(1), *input.shape[2:], int(order), stream)
+    return out
+
+
+def deform_2d(input, weight, bias, offset, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,
+              dilation_w, group, deformable_groups, im2col_step, order):
+    return _deform("deform_2d", 2, input, weight, bias, offset,
+                   ((kernel_h, kernel_w), (stride_h, stride_w), (pad_h, pad_w), (dilation_h, dilation_w)),
+                   group, deformable_groups, order)
+
+
+def deform_3d(input, weight, bias, offset, kernel_d, kernel_h, kernel_w, stride_d, stride_h, stride_w, pad_d, pad_h,
+              pad_w, dilation_d, dilation_h, dilation_w, group, deformable_groups, im2col_step, order):
+    return _deform("deform_3d", 3, input, weight, bias, offset,
+                   ((kernel_d, kernel_h, kernel_w), (stride_d, stride_h, stride_w), (pad_d, pad_h, pad_w),
+                    (dilation_d, dilation_h, dilation_w)), group, deformable_groups, order)

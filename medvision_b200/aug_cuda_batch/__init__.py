@@ -1,10 +1,10 @@
 from .base import BatchCudaAugBase
 from .aug_spatial import (BatchCudaResize, BatchCudaRandomAffine, BatchCudaRandomScale, BatchCudaRandomShift,
-                          BatchCudaRandomRotate, BatchCudaCropRandomWithAffine, BatchCudaCropCenterWithAffine,
+                          BatchCudaRandomRotate, BatchCudaRandomElasticDeformation, BatchCudaCropRandomWithAffine, BatchCudaCropCenterWithAffine,
                           BatchCudaCropForegroundWithAffine, BatchCudaCropDetWithAffine,
                           BatchCudaCropFirstDetWithAffine)
 
 __all__ = ['BatchCudaAugBase', 'BatchCudaResize', 'BatchCudaRandomAffine', 'BatchCudaRandomScale',
-           'BatchCudaRandomShift', 'BatchCudaRandomRotate', 'BatchCudaCropRandomWithAffine',
+           'BatchCudaRandomShift', 'BatchCudaRandomRotate', 'BatchCudaRandomElasticDeformation', 'BatchCudaCropRandomWithAffine',
            'BatchCudaCropCenterWithAffine', 'BatchCudaCropForegroundWithAffine', 'BatchCudaCropDetWithAffine',
            'BatchCudaCropFirstDetWithAffine']

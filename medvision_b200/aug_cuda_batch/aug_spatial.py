@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from .base import BatchCudaAugBase
-from ..ops.cuda_fun_tools import affine_2d, affine_3d
+from ..ops.cuda_fun_tools import affine_2d, affine_3d, apply_offset_2d, apply_offset_3d
 
 
 def _resample_fields(result, dim, rois, out_size, sampling_ratio, order):
@@ -168,6 +168,97 @@ class BatchCudaRandomShift(BatchCudaRandomAffine):
 class BatchCudaRandomRotate(BatchCudaRandomAffine):
     def __init__(self, p, rotate: Union[float, list, tuple], sampling_ratio=1):
         super().__init__(p, scale=0, shift=0, rotate=rotate, sampling_ratio=sampling_ratio)
+
+
+class BatchCudaRandomElasticDeformation(BatchCudaAugBase):
+    """Random smooth warp, as medvision/aug_cuda_batch/aug_spatial.py:204-313: a coarse grid of
+    ``num_control_points`` random displacements per sample (at most ``max_displacement`` half grid
+    cells, the two outermost control points of every axis locked to zero) is blown up to a dense
+    (B, dim, *image_shape) field by one ``affine_*`` resample (order ``order``, Catmull-Rom by
+    default) and applied with ``apply_offset_*``: linear for images, nearest for labels.  The dense
+    field is built once per call and shared by all fields; ``backward`` negates the coarse field."""
+
+    def __init__(self, p, num_control_points=8, max_displacement: float = 0.8, order=3):
+        super().__init__()
+        self.p = p
+        self.num_control_points = num_control_points  # d, h, w order
+        self.max_displacement = max_displacement
+        self.INTER_ORDER = order
+        self.num_locked_borders = 2
+        assert max_displacement <= 1.0
+        self.tmp_params = None
+
+    def __repr__(self):
+        return self.__class__.__name__ + "(p={}, num_control_points={}, max_displacement={})".format(
+            self.p, self.num_control_points, self.max_displacement)
+
+    @property
+    def canBackward(self):
+        return True
+
+    def _forward_params(self, result):
+        self.tmp_params = None
+        self._init_params(result)
+        grid_shape = self.to_tuple(self.num_control_points, self.dim)
+        reach = self.max_displacement * (np.array(self.image_shape) / (np.array(grid_shape) - 1)) / 2
+        fields = []
+        for _ in range(self.batch):
+            coarse = 2 * np.random.rand(*grid_shape, self.dim).astype(np.float32) - 1  # [-1, 1)
+            coarse *= reach.astype(np.float32)
+            for axis in range(self.dim):
+                locked = [slice(None)] * self.dim
+                for i in range(self.num_locked_borders):
+                    for pos in (i, -1 - i):
+                        locked[axis] = pos
+                        coarse[tuple(locked)] = 0
+            fields.append(coarse)
+        self.params = np.array(fields)
+        result[self.key_name] = self.params
+
+    def _backward_params(self, result):
+        self.tmp_params = None
+        self._init_params(result)
+        params = result.pop(self.key_name, None)
+        if params is not None:
+            self.params = -params
+
+    def dense_field(self, device):
+        """(B, dim, *image_shape) float32 displacement field on ``device``."""
+        if self.tmp_params is None:
+            # channels first; halved to smooth
+            coarse = torch.from_numpy(self.params).permute(0, self.dim + 1, *range(1, self.dim + 1)) / 2
+            grid = coarse.shape[2:]
+            index = torch.arange(self.batch, dtype=torch.float32).unsqueeze(-1)
+            center = torch.tensor([i / 2 for i in grid[::-1]], dtype=torch.float32)
+            shape = torch.tensor(list(grid[::-1]), dtype=torch.float32) - (2 * self.num_locked_borders - 1)
+            angles = torch.zeros(1 if self.dim == 2 else 3)
+            boxes = torch.cat([center, shape, angles]).unsqueeze(0).repeat(self.batch, 1)
+            rois = torch.cat([index, boxes], dim=-1).to(device)
+            fn = affine_2d if self.dim == 2 else affine_3d
+            self.tmp_params = fn(coarse.contiguous().to(device), rois, tuple(self.image_shape), 1, 1, True,
+                                 self.INTER_ORDER)
+        return self.tmp_params
+
+    def elastic_transform(self, image: torch.Tensor, order=1):
+        field = self.dense_field(image.device)
+        if order == 0:
+            image = image.to(self.img_type)
+        image = (apply_offset_2d if self.dim == 2 else apply_offset_3d)(image, field, order=order)
+        if order == 0:
+            image = image.int()
+        return image
+
+    def apply_to_img(self, result):
+        for key in result.get('img_fields', []):
+            result[key] = self.elastic_transform(result[key])
+
+    def apply_to_seg(self, result):
+        for key in result.get('seg_fields', []):
+            result[key] = self.elastic_transform(result[key], order=0).int()
+
+    def apply_to_det(self, result):
+        for key in result.get('det_fields', []):
+            raise NotImplementedError
 
 
 class BatchCudaCropRandomWithAffine(BatchCudaAugBase):

@@ -36,3 +36,32 @@ def affine_3d(features, rois, out_size, spatial_scale, sampling_ratio=0, aligned
     """Resample rotated rois of (N, C, D, H, W) ``features`` to (R, C, out_d, out_h, out_w).
     rois: (R, 10) = (batch_index, center_x, center_y, center_z, w, h, d, angle_x, angle_y, angle_z)."""
     return _affine(3, features, rois, out_size, spatial_scale, sampling_ratio, aligned, order)
+
+
+def _apply_offset(ndim, img, offset, order):
+    assert img.shape[2:] == offset.shape[2:]
+    assert offset.shape[1] == ndim
+    channels = img.shape[1]
+    # signature-compatible call of the extension function (identity weight, zero bias, 1x1 kernel);
+    # neither tensor is read by the kernel, so they are not materialised on the device
+    weight = torch.empty((channels, channels) + (1,) * ndim, device='meta')
+    bias = torch.empty(channels, device='meta')
+    offset = offset.to(device=img.device, dtype=img.dtype)
+    ones, zeros = (1,) * ndim, (0,) * ndim
+    fn = _C.deform_2d if ndim == 2 else _C.deform_3d
+    output = fn(img.contiguous(), weight, bias, offset.contiguous(), *ones, *ones, *zeros, *ones, 1, 1, 64, order)
+    assert img.shape == output.shape, f"input is {img.shape}, out is {output.shape}"
+    return output
+
+
+def apply_offset_2d(img, offset, order=1):
+    """Warp ``img`` (B, C, H, W) by the displacement field ``offset`` (B, 2, H, W) = (dh, dw) in pixels:
+    out[b, c, h, w] = interp(img[b, c], (h + dh, w + dw)).  Same signature as
+    medvision/ops/cuda_fun_tools.py:94."""
+    return _apply_offset(2, img, offset, order)
+
+
+def apply_offset_3d(img, offset, order=1):
+    """3D: ``img`` (B, C, D, H, W), ``offset`` (B, 3, D, H, W) = (dd, dh, dw).  Same signature as
+    medvision/ops/cuda_fun_tools.py:133."""
+    return _apply_offset(3, img, offset, order)

@@ -680,6 +680,71 @@ typename A::T hermite_3d(const void* vol, int64_t base, int D, int H, int W, typ
   return val;
 }
 
+// ------------------------------------------------------------------ displacement-field warp
+// medvision/ops/cuda_fun_tools.py:94-167 apply_offset_2d/3d -> deform_2d/deform_3d with a 1x1(x1)
+// kernel, stride 1, no padding, one deformable group, identity weight and zero bias.  The
+// deformable im2col (medvision/csrc/cuda_aug/deform_3d_cuda_kernel.cuh:44-90, the 2D file alike)
+// writes, for voxel p of channel c, interp(img[b, c], (T)p + offset[b, :, p]) when every
+// coordinate lies strictly inside (-1, size) and 0 otherwise; offset channels are (d, h, w) /
+// (h, w).  The addmm with the identity weight and the zero bias (deform_3d_cuda.cu:118-146)
+// returns a finite column value unchanged, so it is not restated.
+struct OffsetArgs {
+  const void* img;
+  const void* off;
+  void* out;
+  int ndim;
+  int64_t B, C, D, H, W;
+  int order, fma_mode, nthreads;
+};
+
+template <class A>
+int run_offset(const OffsetArgs& a) {
+  typedef typename A::T T;
+  const int64_t vol = a.D * a.H * a.W;
+  parallel_for(a.B * a.D * a.H, a.nthreads, [&](int64_t row) {
+    const int64_t b = row / (a.D * a.H);
+    const int d = (int)((row / a.H) % a.D), h = (int)(row % a.H);
+    for (int w = 0; w < (int)a.W; ++w) {
+      const int64_t s = ((int64_t)d * a.H + h) * a.W + w;
+      const int64_t ob = b * a.ndim * vol + s;
+      T z = (T)0, y, x;
+      if (a.ndim == 3) {
+        z = A::add(A::fi(d), A::ld(a.off, ob));
+        y = A::add(A::fi(h), A::ld(a.off, ob + vol));
+        x = A::add(A::fi(w), A::ld(a.off, ob + 2 * vol));
+      } else {
+        y = A::add(A::fi(h), A::ld(a.off, ob));
+        x = A::add(A::fi(w), A::ld(a.off, ob + vol));
+      }
+      const bool in = (double)y > -1.0 && (double)x > -1.0 && (double)y < (double)a.H && (double)x < (double)a.W &&
+                      (a.ndim == 2 || ((double)z > -1.0 && (double)z < (double)a.D));
+      T wt[8];
+      int64_t off[8];
+      const int n = a.ndim == 3 ? 8 : 4;
+      if (in && a.order != 3) {
+        if (a.ndim == 3) taps_3d<A>((int)a.D, (int)a.H, (int)a.W, z, y, x, a.order, wt, off);
+        else taps_2d<A>((int)a.H, (int)a.W, y, x, a.order, wt, off);
+      }
+      for (int64_t c = 0; c < a.C; ++c) {
+        const int64_t base = (b * a.C + c) * vol;
+        T val = (T)0;
+        if (in) {
+          if (a.order == 3) {
+            val = a.ndim == 3 ? hermite_3d<A>(a.img, base, (int)a.D, (int)a.H, (int)a.W, z, y, x, a.fma_mode)
+                              : hermite_2d<A>(a.img, base, (int)a.H, (int)a.W, y, x, a.fma_mode);
+          } else {
+            T v[8];
+            for (int k = 0; k < n; ++k) v[k] = A::ld(a.img, base + off[k]);
+            val = tap_sum<A>(wt, v, n, a.fma_mode);
+          }
+        }
+        A::st(a.out, base + s, val);
+      }
+    }
+  });
+  return 0;
+}
+
 int check(const Args& a, int dtype, bool fwd) {
   if (dtype != DT_F32 && dtype != DT_F16 && dtype != DT_F64) return -1;
   if (a.ndim != 2 && a.ndim != 3) return -2;
@@ -727,6 +792,21 @@ int mvr_oracle_bwd(const void* grad_out, const void* rois, void* grad_in, int dt
     case DT_F32: return run_bwd<Arith<DT_F32> >(a);
     case DT_F16: return run_bwd<Arith<DT_F16> >(a);
     default: return run_bwd<Arith<DT_F64> >(a);
+  }
+}
+
+// img / out (B, C, [D,] H, W), offset (B, ndim, [D,] H, W); D = 1 for ndim 2.
+int mvr_oracle_offset(const void* img, const void* offset, void* out, int dtype, int ndim, int64_t B, int64_t C,
+                      int64_t D, int64_t H, int64_t W, int order, int fma_mode, int nthreads) {
+  if (dtype != DT_F32 && dtype != DT_F16 && dtype != DT_F64) return -1;
+  if (ndim != 2 && ndim != 3) return -2;
+  if (order != 0 && order != 1 && order != 3) return -4;
+  if ((ndim == 2 && D != 1) || B < 0 || C < 0 || D < 1 || H < 1 || W < 1) return -6;
+  OffsetArgs a = {img, offset, out, ndim, B, C, D, H, W, order, fma_mode, nthreads};
+  switch (dtype) {
+    case DT_F32: return run_offset<Arith<DT_F32> >(a);
+    case DT_F16: return run_offset<Arith<DT_F16> >(a);
+    default: return run_offset<Arith<DT_F64> >(a);
   }
 }
 

@@ -36,6 +36,8 @@ def lib():
         L.mvr_oracle_bwd.restype = i32
         L.mvr_oracle_bwd.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64, i64,
                                      i32, i32, i32, f32, i32, i32, i32, i32, i32, i32, vp]
+        L.mvr_oracle_offset.restype = i32
+        L.mvr_oracle_offset.argtypes = [vp, vp, vp, i32, i32, i64, i64, i64, i64, i64, i32, i32, i32]
         L.mvr_oracle_max_threads.restype = i32
         _lib = L
     return _lib
@@ -122,3 +124,21 @@ def backward(grad_out, rois, feature_size, kind, spatial_scale=1.0, sampling_rat
     if rc == 1:
         raise IndexError("roi batch index outside [0, N)")
     return grad_in
+
+
+def apply_offset(img, offset, order=1, fma_mode=0, nthreads=0):
+    """CPU restatement of ``apply_offset_2d/3d`` (medvision/ops/cuda_fun_tools.py:94-167):
+    img (B, C, [D,] H, W), offset (B, ndim, [D,] H, W) in the image's dtype."""
+    img = img.detach().cpu().contiguous()
+    offset = offset.detach().cpu().to(img.dtype).contiguous()
+    ndim = img.dim() - 2
+    assert tuple(offset.shape) == (img.shape[0], ndim) + tuple(img.shape[2:])
+    B, C = img.shape[:2]
+    D = img.shape[2] if ndim == 3 else 1
+    H, W = img.shape[-2:]
+    out = torch.empty_like(img)
+    rc = lib().mvr_oracle_offset(img.data_ptr(), offset.data_ptr(), out.data_ptr(), DTYPES[img.dtype], ndim,
+                                 B, C, D, H, W, order, fma_mode, nthreads)
+    if rc < 0:
+        raise ValueError("mvr_oracle_offset: argument error %d" % rc)
+    return out

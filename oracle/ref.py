@@ -3,7 +3,7 @@
 Loader for ``oracle/_ref/mvref_C*.so``: the reference's own CUDA kernels of the resampling
 path, compiled unmodified for sm_100a by ``make -C oracle ref`` (which needs the reference
 checkout; the built file travels with the repository snapshot, the checkout does not).
-Exposes the ten functions under the names ``medvision._C`` gives them, plus thin wrappers
+Exposes the functions under the names ``medvision._C`` gives them, plus thin wrappers
 that allocate the result the way the reference's Python layer does.
 """
 import glob
@@ -72,3 +72,25 @@ def backward(grad_out, rois, feature_size, kind, spatial_scale=1.0, sampling_rat
             fn(grad_out.contiguous(), rois, grad_in, *out_size, spatial_scale, sampling_ratio, aligned, order)
         torch.cuda.synchronize()
     return grad_in
+
+
+def apply_offset(img, offset, order=1):
+    """The reference's ``apply_offset_2d/3d`` (medvision/ops/cuda_fun_tools.py:94-167) on CUDA
+    tensors: identity weight, zero bias, 1x1(x1) kernel, stride 1, one deformable group."""
+    m = module()
+    ndim = img.dim() - 2
+    assert offset.shape[1] == ndim and img.shape[2:] == offset.shape[2:]
+    channels = img.shape[1]
+    weight = torch.eye(channels, channels, device=img.device).reshape((channels, channels) + (1,) * ndim)
+    bias = torch.zeros(channels, device=img.device)
+    offset = offset.to(img.device)
+    if img.dtype == torch.float16:
+        offset, bias, weight = offset.half(), bias.half(), weight.half()
+    ones, zeros = (1,) * ndim, (0,) * ndim
+    fn = m.deform_2d if ndim == 2 else m.deform_3d
+    with torch.cuda.device(img.device):
+        torch.cuda.current_stream().synchronize()
+        out = fn(img.contiguous(), weight.contiguous(), bias.contiguous(), offset.contiguous(),
+                 *ones, *ones, *zeros, *ones, 1, 1, 64, order)
+        torch.cuda.synchronize()
+    return out

@@ -4,10 +4,10 @@
 // REF_SRC (e.g. "cuda/roi_align_rotated_3d_cuda.cu", relative to medvision/csrc of
 // the reference checkout) is compiled unmodified, where it lies: it is pulled in by
 // #include, never copied.  The only obstacle to building it against a current torch
-// is that its launchers spell the dispatch key `tensor.type()`; all torch headers
-// the reference needs are therefore included FIRST (their include guards keep them
-// from being re-read), and the identifier `type` is then mapped to `scalar_type`
-// for the reference's own tokens only.
+// is that its launchers pass `tensor.type()` (an at::DeprecatedTypeProperties) as the
+// dispatch key, which AT_DISPATCH_* no longer accepts; the overload below, declared in
+// the namespace where the dispatch macros look their helper up, restores that form
+// without touching a single token of the reference.
 #include <torch/extension.h>
 #include <cuda.h>
 #include <float.h>
@@ -22,6 +22,8 @@
 #error "compile with -DREF_SRC='\"cuda/<launcher>.cu\"'"
 #endif
 
-#define type scalar_type
+namespace detail {
+inline at::ScalarType scalar_type(const at::DeprecatedTypeProperties& t) { return t.scalarType(); }
+}  // namespace detail
+
 #include REF_SRC
-#undef type

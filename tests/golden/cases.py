@@ -77,3 +77,37 @@ def make_inputs(case):
     rois = rois.to(dtype)
     grad = torch.randn((case["R"], case["C"]) + tuple(case["out_size"]), generator=gen, dtype=torch.float64).to(dtype)
     return feat, rois, grad
+
+
+def offset_cases():
+    """(name, dict) for the displacement-field warp (apply_offset_2d/3d) golden cases."""
+    out = []
+    seed = 500
+    for ndim in (2, 3):
+        for spatial in (((20, 24), (7, 13)) if ndim == 2 else ((9, 12, 14), (5, 6, 7))):
+            for dtype in (torch.float32, torch.float16):
+                for order in (0, 1, 3):
+                    seed += 1
+                    name = "offset_%dd_%s_%s_o%d" % (ndim, "x".join(map(str, spatial)),
+                                                     "f32" if dtype == torch.float32 else "f16", order)
+                    out.append((name, dict(ndim=ndim, dtype=dtype, order=order, spatial=spatial, seed=seed, B=2, C=3)))
+    return out
+
+
+def make_offset_inputs(case):
+    """Image in [-0.5, 1.5); field = gaussian displacements (sigma 2.5 voxels, so a good share of
+    the samples leaves the image), with a sprinkling of whole-voxel displacements and of samples
+    placed exactly on the borders -1, 0, size-1 and size of the validity test."""
+    gen = torch.Generator().manual_seed(case["seed"])
+    spatial = tuple(case["spatial"])
+    ndim = case["ndim"]
+    img = (torch.rand((case["B"], case["C"]) + spatial, generator=gen, dtype=torch.float64) * 2 - 0.5)
+    off = torch.randn((case["B"], ndim) + spatial, generator=gen, dtype=torch.float64) * 2.5
+    pick = torch.rand(off.shape, generator=gen)
+    off = torch.where(pick < 0.1, off.round(), off)
+    grid = torch.stack(torch.meshgrid(*[torch.arange(n, dtype=torch.float64) for n in spatial], indexing="ij"))[None]
+    sizes = torch.tensor(spatial, dtype=torch.float64).reshape((1, ndim) + (1,) * ndim)
+    for k, target in enumerate((-1.0 + 0 * sizes, 0 * sizes, sizes - 1, sizes)):
+        sel = (pick >= 0.1 + 0.02 * k) & (pick < 0.12 + 0.02 * k)
+        off = torch.where(sel, target - grid, off)
+    return img.to(case["dtype"]), off.to(case["dtype"])

@@ -3,6 +3,7 @@
 Run on a machine with a B200 and a built ``oracle/_ref/mvref_C*.so``:
 
     python tests/golden/make_golden.py [output.npz]
+    python tests/golden/make_golden.py offset          # -> reference_offset_cuda.npz
 
 For every case of ``cases.py`` the seeded inputs go through the reference's forward and
 backward kernels; inputs are NOT stored (they are regenerated from the seed), outputs are.
@@ -27,7 +28,20 @@ def to_np(t):
     return t.view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.float16 else t.numpy()
 
 
+def main_offset():
+    """apply_offset_2d/3d through the reference's deform_2d / deform_3d kernels."""
+    out_path = os.path.join(HERE, "reference_offset_cuda.npz")
+    blobs = {}
+    for name, case in cases.offset_cases():
+        img, off = cases.make_offset_inputs(case)
+        blobs[name] = to_np(ref.apply_offset(img.cuda(), off.cuda(), case["order"]))
+    np.savez_compressed(out_path, **blobs)
+    print("wrote", out_path, len(blobs), "arrays", os.path.getsize(out_path), "bytes")
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "offset":
+        return main_offset()
     out_path = sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "reference_cuda.npz")
     blobs = {}
     for name, case in cases.all_cases():

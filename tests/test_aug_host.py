@@ -8,7 +8,8 @@ import pytest
 import torch
 
 from medvision_b200.aug_cuda_batch import (BatchCudaCropCenterWithAffine, BatchCudaCropRandomWithAffine,
-                                           BatchCudaRandomAffine, BatchCudaRandomRotate, BatchCudaRandomScale,
+                                           BatchCudaRandomAffine, BatchCudaRandomElasticDeformation, BatchCudaRandomRotate,
+                                           BatchCudaRandomScale,
                                            BatchCudaRandomShift, BatchCudaResize)
 
 
@@ -119,3 +120,33 @@ def test_sliding_window_anchors():
     t2 = CudaPatches(patch_size=(6, 6), overlap=0.0)
     t2._forward_params({"img_dim": 2, "img": torch.zeros(3, 5, 13)})
     assert t2.params.tolist() == [[0, 0, 6, 6], [6, 0, 12, 6]]
+
+
+@pytest.mark.parametrize("shape,points", [((2, 1, 16, 24, 32), 8), ((2, 1, 24, 32), (6, 7))])
+def test_elastic_coarse_field_draws_and_locked_borders(shape, points):
+    """Same draws as the reference (one np.random.rand(*grid, dim) per sample), scaled per axis
+    to max_displacement half grid cells, two outermost control points of every axis zeroed."""
+    dim = len(shape) - 2
+    t = BatchCudaRandomElasticDeformation(1.0, num_control_points=points, max_displacement=0.8)
+    np.random.seed(11)
+    res = _result(shape)
+    t._forward_params(res)
+    grid = t.to_tuple(points, dim)
+    assert t.params.shape == (2,) + grid + (dim,) and t.params.dtype == np.float32
+    np.random.seed(11)
+    for b in range(2):
+        draw = 2 * np.random.rand(*grid, dim).astype(np.float32) - 1
+        for d in range(dim):
+            reach = 0.8 * (shape[2 + d] / (grid[d] - 1)) / 2
+            inner = (slice(2, -2),) * dim
+            np.testing.assert_allclose(t.params[b][inner + (d,)], draw[inner + (d,)] * reach, rtol=1e-6)
+            assert np.abs(t.params[b][..., d]).max() <= reach
+    for axis in range(dim):
+        for pos in (0, 1, -1, -2):
+            assert not np.take(t.params, pos, axis=1 + axis).any()
+    assert res[t.key_name] is t.params
+    # backward negates the stored field and forgets the cached dense field
+    t.tmp_params = "stale"
+    t._backward_params(res)
+    assert t.tmp_params is None and t.key_name not in res
+    assert t.canBackward

@@ -116,3 +116,37 @@ def test_sliding_window_patches_are_the_slices():
     for k, (x0, y0, z0, x1, y1, z1) in enumerate(t.params.tolist()):
         assert torch.equal(patches[k], img[:, z0:z1, y0:y1, x0:x1])
         assert torch.equal(seg_patches[k], seg[:, z0:z1, y0:y1, x0:x1])
+
+
+@pytest.mark.parametrize("shape,dtype", [((2, 2, 16, 24, 32), torch.float16), ((2, 2, 16, 24, 32), torch.float32),
+                                         ((3, 1, 40, 48), torch.float32)])
+def test_elastic_deformation(shape, dtype):
+    """The dense field is one Catmull-Rom affine resample of the coarse field; the image is warped
+    linearly, the label with nearest; backward uses the negated field."""
+    from medvision_b200.aug_cuda_batch import BatchCudaRandomElasticDeformation
+    dim = len(shape) - 2
+    np.random.seed(5)
+    t = BatchCudaRandomElasticDeformation(1.0, num_control_points=7, max_displacement=0.9)
+    res = _result(shape, dtype, 9)
+    img_in, seg_in = res["img"].clone(), res["gt_seg"].clone()
+    res = t(res)
+    coarse = torch.from_numpy(t.params).permute(0, dim + 1, *range(1, dim + 1)).contiguous() / 2
+    # roi of the blow-up: centred on the grid, 3 control points narrower (the locked border)
+    roi = torch.tensor([[b] + [3.5] * dim + [4.0] * dim + [0.0] * (1 if dim == 2 else 3) for b in range(shape[0])])
+    field = port.forward(coarse, roi, shape[2:], port.KIND_ROTATED, 1.0, 1, True, 3, trig=port.device_trig(roi),
+                         fma_mode=REF_FM)
+    dense = t.dense_field(img_in.device)
+    assert dense.dtype == torch.float32 and dense.shape == (shape[0], dim) + tuple(shape[2:])
+    torch.testing.assert_close(dense.cpu(), field, rtol=1e-5, atol=1e-6)
+    assert float(dense.abs().max()) > 0.5
+    # the warp itself, on the field the GPU built
+    fm = 0 if dtype == torch.float16 else REF_FM
+    assert n_mismatch(res["img"], port.apply_offset(img_in, dense, 1, fma_mode=fm)) == 0
+    want_seg = port.apply_offset(seg_in.to(dtype), dense, 0, fma_mode=fm).int()
+    assert res["gt_seg"].dtype == torch.int32 and torch.equal(res["gt_seg"].cpu(), want_seg)
+    # the inverse pass samples with the negated field
+    warped, warped_seg = res["img"].clone(), res["gt_seg"].clone()
+    back = t.backward(res)
+    assert torch.equal(t.tmp_params, -dense) and t.key_name not in back
+    assert n_mismatch(back["img"], port.apply_offset(warped, -dense, 1, fma_mode=fm)) == 0
+    assert torch.equal(back["gt_seg"].cpu(), port.apply_offset(warped_seg.to(dtype), -dense, 0, fma_mode=fm).int())
