@@ -126,6 +126,10 @@ class Ours:
     def public_forward(self, feat, rois, out_size, order):
         return self.affine_3d(feat, rois, tuple(out_size), 1.0, 1, True, order)
 
+    def apply_offset(self, img, field, order):
+        from medvision_b200.ops import apply_offset_3d
+        return apply_offset_3d(img, field, order)
+
     def host_forward(self, feat_h, rois_h, out_size, order, out_h):
         """host tensors in, host tensor out: the library's pipelined entry point"""
         from medvision_b200.ops import affine_from_host
@@ -150,6 +154,10 @@ class ReferenceCuda:
         out = feat.new_zeros((rois.size(0), feat.size(1)) + tuple(out_size))
         self.m.affine_3d(feat, rois.type(feat.type()), out, *out_size, 1.0, 1, True, order)
         return out
+
+    def apply_offset(self, img, field, order):
+        from oracle import ref
+        return ref.apply_offset(img, field, order)
 
 
 # ----------------------------------------------------------------------------- measurement
@@ -357,6 +365,38 @@ def detection_configs(impl_name):
     return res
 
 
+def elastic_config(impl, peak):
+    """The elastic deformation's two resampling steps on 4 CT-like half volumes (1,128,256,256):
+    blowing the 8^3 control grid up to the dense displacement field (affine_3d, Catmull-Rom) and
+    warping the image with it (apply_offset_3d, linear), as BatchCudaRandomElasticDeformation does."""
+    shape = (4, 1, 128, 256, 256)
+    img = ct_like(shape, 77, "cuda")
+    g = torch.Generator().manual_seed(78)
+    reach = torch.tensor([0.8 * n / 7 / 2 for n in shape[2:]]).reshape(1, 3, 1, 1, 1)
+    coarse = (torch.rand((4, 3, 8, 8, 8), generator=g) * 2 - 1) * reach / 2
+    for axis in (2, 3, 4):
+        for pos in (0, 1, -1, -2):
+            coarse.select(axis, pos).zero_()
+    coarse = coarse.cuda()
+    rois = torch.tensor([[b, 4, 4, 4, 5, 5, 5, 0, 0, 0] for b in range(4)], dtype=torch.float32).cuda()
+    field = impl.public_forward(coarse, rois, shape[2:], 3)
+    n = img.numel()
+    res = []
+    ms = time_steps(lambda: impl.public_forward(coarse, rois, shape[2:], 3), 20, 5, 1) / 20
+    res.append({"workload": "elastic: control grid (4,3,8,8,8) fp32 -> dense field (4,3,128,256,256), affine_3d order 3",
+                "pass": "fwd", "ms_per_step": ms, "gvoxel_per_s": field.numel() / (ms * 1e-3) / 1e9,
+                "algorithmic_bytes": 4 * field.numel(), "achieved_gbs": 4 * field.numel() / (ms * 1e-3) / 1e9,
+                "frac_of_peak": 4 * field.numel() / (ms * 1e-3) / 1e9 / peak, "note": "input fits in L1; store-bound"})
+    ms = time_steps(lambda: impl.apply_offset(img, field, 1), 20, 5, 1) / 20
+    # field converted to half (3 x 4 B read, 3 x 2 B written) by the public call, then 3 x 2 B + image 2 B read, 2 B written
+    alg = n * (3 * 2 + 2 + 2)
+    res.append({"workload": "elastic: apply_offset_3d fp16 (4,1,128,256,256), fp32 field, linear", "pass": "fwd",
+                "ms_per_step": ms, "gvoxel_per_s": n / (ms * 1e-3) / 1e9, "algorithmic_bytes": alg,
+                "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac_of_peak": alg / (ms * 1e-3) / 1e9 / peak,
+                "note": "public call incl. the field's fp32->fp16 cast; bytes counted for the warp kernel only"})
+    return res
+
+
 def cpu_baseline_scipy():
     """What the reference's numpy augmentations call for the same job
     (medvision/aug_cpu/aug_spatial.py:475 rotate, :99 zoom), single-threaded scipy."""
@@ -440,7 +480,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c5")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["elastic"], default="c5",
+                    help="elastic: only the elastic deformation's two steps, one GPU (profiling aid)")
     ap.add_argument("--small", action="store_true", help="reduced copy of the workload (for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true", help="skip e2e, CPU baselines and the extra configurations")
     ap.add_argument("--backward", action="store_true", help="time forward + backward instead of forward (profiling aid)")
@@ -457,6 +498,10 @@ def main():
 
     rank, world, local = dist_setup(args.gpus)
     impl = Ours() if args.impl == "ours" else ReferenceCuda()
+    if args.workload == "elastic":
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "elastic": elastic_config(impl, load_peaks()[0])}))
+        return
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()  # started early: the tool needs a moment before its first sample
@@ -526,6 +571,7 @@ def main():
                               "gvoxel_per_s": n2 / (m2 * 1e-3) / 1e9, "algorithmic_bytes": b2,
                               "achieved_gbs": b2 / (m2 * 1e-3) / 1e9, "frac_of_peak": b2 / (m2 * 1e-3) / 1e9 / peak,
                               "note": "input fits in L2" if key == "c4" else "input larger than L2"})
+            extra += elastic_config(impl, peak)
             det = detection_configs(args.impl)
             if det:
                 extra += det

@@ -10,6 +10,7 @@
 #include "mvr_tma3d.cuh"
 #include "mvr_bwd3d.cuh"
 #include "mvr_offset.cuh"
+#include "mvr_cubic3d.cuh"
 
 // ---- scratch of the entry point that allocates nothing ------------------------------------
 // Lives in the library image: every GPU that loads the library holds these 16 MiB until the
@@ -113,6 +114,16 @@ int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
   {
     const int rc = fwd ? try_launch_stream3d(p, dtype, st) : try_launch_bwd_stream3d(p, dtype, st);
     if (rc != MVR_STREAM3D_NOT_APPLICABLE) return rc;
+  }
+  if (fwd && p.order == 3 && p.ndim == 3) {
+    int rc;
+    switch (dtype) {
+      case MVR_F32: rc = launch_cubic3d<float>(p, st); break;
+      case MVR_F16: rc = launch_cubic3d<__half>(p, st); break;
+      default: rc = launch_cubic3d<double>(p, st); break;
+    }
+    if (rc < 0) return MVR_ERR_TOO_LARGE;
+    if (rc == 0) return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
   }
   switch (dtype) {
     case MVR_F32: return launch_generic<float>(p, fwd, st);

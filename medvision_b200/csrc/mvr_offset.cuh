@@ -27,20 +27,11 @@ struct OffsetParams {
 
 constexpr int kOffsetThreads = 256;
 
-template <typename T, int NDIM>
-__global__ void __launch_bounds__(kOffsetThreads)
-apply_offset_kernel(const OffsetParams p) {
+template <typename T, int NDIM, bool CUBIC>
+__device__ __forceinline__ void apply_offset_pair(const OffsetParams& p, int b, int d, int h, int wp) {
   typedef Ar<T> A;
   typedef P2<T> Q;
   typedef typename Q::V V;
-  const int pairs_w = (p.W + 1) >> 1;
-  const long long total = (long long)p.B * p.D * p.H * pairs_w;
-  const long long idx = (long long)blockIdx.x * kOffsetThreads + threadIdx.x;
-  if (idx >= total) return;
-  const int wp = (int)(idx % pairs_w);
-  const int h = (int)((idx / pairs_w) % p.H);
-  const int d = (int)((idx / ((long long)pairs_w * p.H)) % p.D);
-  const int b = (int)(idx / ((long long)pairs_w * p.H * p.D));
   const int w0 = wp * 2;
   const bool has_b = w0 + 1 < p.W;
   const long long vol = (long long)p.D * p.H * p.W;
@@ -76,7 +67,7 @@ apply_offset_kernel(const OffsetParams p) {
   T* out = (T*)p.out + (long long)b * p.C * vol + s0;
   const V zero2 = Q::dup(zero);
 
-  if (p.order == 3) {  // Catmull-Rom: per voxel
+  if (CUBIC) {  // Catmull-Rom: per voxel
     for (int c = 0; c < p.C; ++c, img += vol, out += vol) {
       T va = zero, vb = zero;
       if (NDIM == 3) {
@@ -112,6 +103,7 @@ apply_offset_kernel(const OffsetParams p) {
   } else {
     w[0] = Q::mul(ty.h, tx.h); w[1] = Q::mul(ty.h, tx.l); w[2] = Q::mul(ty.l, tx.h); w[3] = Q::mul(ty.l, tx.l);
   }
+#pragma unroll 1
   for (int c = 0; c < p.C; ++c, img += vol, out += vol) {
     const T* pa = img + ba;
     const T* pb = img + bb;
@@ -141,14 +133,37 @@ apply_offset_kernel(const OffsetParams p) {
   (void)zero2;
 }
 
+template <typename T, int NDIM, bool CUBIC>
+__global__ void __launch_bounds__(kOffsetThreads, CUBIC ? 1 : 4)
+apply_offset_kernel(const OffsetParams p) {
+  typedef Ar<T> A;
+  typedef P2<T> Q;
+  typedef typename Q::V V;
+  // grid.x covers the voxel pairs of one sample (fewer than 2^30), grid.y strides over the batch
+  const unsigned pairs_w = (unsigned)(p.W + 1) >> 1;
+  const unsigned per_sample = (unsigned)p.D * (unsigned)p.H * pairs_w;
+  const unsigned idx = blockIdx.x * (unsigned)kOffsetThreads + threadIdx.x;
+  if (idx >= per_sample) return;
+  const int wp = (int)(idx % pairs_w);
+  const unsigned row = idx / pairs_w;
+  const int h = (int)(row % (unsigned)p.H);
+  const int d = (int)(row / (unsigned)p.H);
+  for (int b = blockIdx.y; b < p.B; b += gridDim.y) apply_offset_pair<T, NDIM, CUBIC>(p, b, d, h, wp);
+}
+
 template <int NDIM>
 inline int launch_apply_offset(const OffsetParams& p, int dtype, cudaStream_t st) {
-  const long long total = (long long)p.B * p.D * p.H * ((p.W + 1) / 2);
-  if (total == 0 || p.C == 0) return 0;
-  const long long blocks = (total + kOffsetThreads - 1) / kOffsetThreads;
-  if (blocks > 0x7fffffffLL) return -9;
-  if (dtype == 0) apply_offset_kernel<float, NDIM><<<(unsigned)blocks, kOffsetThreads, 0, st>>>(p);
-  else apply_offset_kernel<__half, NDIM><<<(unsigned)blocks, kOffsetThreads, 0, st>>>(p);
+  const long long per_sample = (long long)p.D * p.H * ((p.W + 1) / 2);
+  if (per_sample == 0 || p.B == 0 || p.C == 0) return 0;
+  const dim3 grid((unsigned)((per_sample + kOffsetThreads - 1) / kOffsetThreads), (unsigned)min(p.B, 65535));
+  const bool cubic = p.order == 3;
+  if (dtype == 0) {
+    if (cubic) apply_offset_kernel<float, NDIM, true><<<grid, kOffsetThreads, 0, st>>>(p);
+    else apply_offset_kernel<float, NDIM, false><<<grid, kOffsetThreads, 0, st>>>(p);
+  } else {
+    if (cubic) apply_offset_kernel<__half, NDIM, true><<<grid, kOffsetThreads, 0, st>>>(p);
+    else apply_offset_kernel<__half, NDIM, false><<<grid, kOffsetThreads, 0, st>>>(p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
