@@ -196,18 +196,20 @@ int mvr_affine_3d(const void* input, const void* rois, void* output, int dtype,
 
 /* out[b, c, p] = interp(img[b, c], p + offset[b, :, p]) for every voxel p; float32 / float16;
  * order 0, 1 or 3.  img and out are (B, C, H, W), offset is (B, 2, H, W) with the displacement
- * along h, then w, in pixels.
+ * along h, then w, in pixels.  offset_dtype is the field's element type: the image's, or
+ * MVR_F32 with a half image -- the field is then rounded to half as it is read, which is what
+ * the reference's `offset = offset.half()` (cuda_fun_tools.py:116-119) does in a pass of its own.
  * Replaces, for the one way the reference uses it (medvision/ops/cuda_fun_tools.py:94-130
  * apply_offset_2d: 1x1 kernel, stride 1, no padding, identity weight, zero bias),
  * medvision/csrc/vision.cpp:76 deform_2d(input, weight, bias, offset, ...) -> deform_2d.h ->
  * cuda_aug/deform_2d_cuda.cu (deformable im2col + addmm + permute). */
-int mvr_apply_offset_2d(const void* img, const void* offset, void* out, int dtype, int64_t B, int64_t C, int64_t H,
-                        int64_t W, int order, void* stream);
+int mvr_apply_offset_2d(const void* img, const void* offset, void* out, int dtype, int offset_dtype, int64_t B,
+                        int64_t C, int64_t H, int64_t W, int order, void* stream);
 /* 3D: img / out (B, C, D, H, W), offset (B, 3, D, H, W) = displacement along d, h, w.
  * Replaces medvision/csrc/vision.cpp:77 deform_3d as used by apply_offset_3d
  * (medvision/ops/cuda_fun_tools.py:133-167, cuda_aug/deform_3d_cuda.cu:44-152). */
-int mvr_apply_offset_3d(const void* img, const void* offset, void* out, int dtype, int64_t B, int64_t C, int64_t D,
-                        int64_t H, int64_t W, int order, void* stream);
+int mvr_apply_offset_3d(const void* img, const void* offset, void* out, int dtype, int offset_dtype, int64_t B,
+                        int64_t C, int64_t D, int64_t H, int64_t W, int order, void* stream);
 
 #ifdef __cplusplus
 }

@@ -154,6 +154,35 @@ def affine_3d(input, rois, output, aligned_depth, aligned_height, aligned_width,
          (aligned_depth, aligned_height, aligned_width), spatial_scale, sampling_ratio, aligned, order, True)
 
 
+def apply_offset(input, offset, order):
+    """Displacement-field warp: ``out[b, c, p] = interp(input[b, c], p + offset[b, :, p])``.  Not a
+    function of the reference's extension: it is what ``deform_2d`` / ``deform_3d`` compute in the
+    configuration ``apply_offset_2d/3d`` call them with.  A float32 field with a half image is
+    rounded to half as it is read (the reference casts it in a pass of its own)."""
+    ndim = input.dim() - 2
+    name = "deform_%dd" % ndim
+    if not input.is_cuda:
+        raise RuntimeError("Not implemented on the CPU")
+    if ndim not in (2, 3) or offset.dim() != ndim + 2 or offset.size(1) != ndim or \
+            offset.shape[2:] != input.shape[2:] or offset.size(0) != input.size(0):
+        raise RuntimeError(f"{name}: offset must be (B, {ndim}, *spatial) for input (B, C, *spatial)")
+    if offset.device != input.device:
+        raise RuntimeError("expected all tensors to be on the same CUDA device")
+    if input.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError(f'"{name}" not implemented for \'{str(input.dtype).replace("torch.", "")}\'')
+    if offset.dtype != input.dtype and not (input.dtype == torch.float16 and offset.dtype == torch.float32):
+        raise RuntimeError(f"expected scalar type {input.dtype} but found {offset.dtype}")
+    assert input.is_contiguous(), "input tensor has to be contiguous"
+    offset = offset.contiguous()
+    out = torch.empty_like(input)
+    fn = getattr(_lib.lib, "mvr_apply_offset_%dd" % ndim)
+    with torch.cuda.device(input.device):
+        stream = torch.cuda.current_stream(input.device).cuda_stream
+        _call(fn, input.data_ptr(), offset.data_ptr(), out.data_ptr(), _DTYPES[input.dtype], _DTYPES[offset.dtype],
+              input.size(0), input.size(1), *input.shape[2:], int(order), stream)
+    return out
+
+
 def _deform(name, ndim, input, weight, bias, offset, geometry, group, deformable_groups, order):
     """The reference's ``deform_2d`` / ``deform_3d`` (medvision/csrc/vision.cpp:76-77) for the one
     configuration its Python layer uses (medvision/ops/cuda_fun_tools.py:94-167): 1x1(x1) kernel,
@@ -166,24 +195,14 @@ def _deform(name, ndim, input, weight, bias, offset, geometry, group, deformable
         raise NotImplementedError(f"{name}: only the 1x1 identity configuration of apply_offset_* is provided")
     if not input.is_cuda:
         raise RuntimeError("Not implemented on the CPU")
+    if input.dim() != ndim + 2:
+        raise RuntimeError(f"{name}: expected a {ndim + 2}-D input")
     if tuple(weight.shape) != (input.size(1), input.size(1)) + (1,) * ndim:
         raise NotImplementedError(f"{name}: the weight must be the channel identity")
-    if input.dim() != ndim + 2 or offset.dim() != ndim + 2 or offset.size(1) != ndim or \
-            offset.shape[2:] != input.shape[2:] or offset.size(0) != input.size(0):
-        raise RuntimeError(f"{name}: offset must be (B, {ndim}, *spatial) for input (B, C, *spatial)")
-    if offset.dtype != input.dtype or offset.device != input.device:
+    if offset.dtype != input.dtype:
+        # the reference reinterprets with tensor.data<scalar_t>(), which throws on a mismatch
         raise RuntimeError(f"expected scalar type {input.dtype} but found {offset.dtype}")
-    if input.dtype not in (torch.float32, torch.float16):
-        raise RuntimeError(f'"{name}" not implemented for \'{str(input.dtype).replace("torch.", "")}\'')
-    assert input.is_contiguous(), "input tensor has to be contiguous"
-    offset = offset.contiguous()
-    out = torch.empty_like(input)
-    fn = getattr(_lib.lib, "mvr_apply_offset_%dd" % ndim)
-    with torch.cuda.device(input.device):
-        stream = torch.cuda.current_stream(input.device).cuda_stream
-        _call(fn, input.data_ptr(), offset.data_ptr(), out.data_ptr(), _DTYPES[input.dtype], input.size(0),
-              input.size(1), *input.shape[2:], int(order), stream)
-    return out
+    return apply_offset(input, offset, order)
 
 
 def deform_2d(input, weight, bias, offset, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,

@@ -39,8 +39,8 @@ PROTOTYPES = {
     "mvr_roi_align_rotated_2d_backward": _ROT2D,
     "mvr_roi_align_rotated_3d_forward": _ROT3D,
     "mvr_roi_align_rotated_3d_backward": _ROT3D,
-    "mvr_apply_offset_2d": [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp],
-    "mvr_apply_offset_3d": [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
+    "mvr_apply_offset_2d": [_vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _vp],
+    "mvr_apply_offset_3d": [_vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
     "mvr_affine_2d": _ROT2D,
     "mvr_affine_3d": _ROT3D,
 }

@@ -240,9 +240,10 @@ int mvr_roi_resample_bwd_noalloc(const void* grad_out, const void* rois, void* g
   }
 }
 
-static int apply_offset_impl(const void* img, const void* offset, void* out, int dtype, int ndim, int64_t B, int64_t C,
-                             int64_t D, int64_t H, int64_t W, int order, void* stream) {
+static int apply_offset_impl(const void* img, const void* offset, void* out, int dtype, int offset_dtype, int ndim,
+                             int64_t B, int64_t C, int64_t D, int64_t H, int64_t W, int order, void* stream) {
   if (dtype != MVR_F32 && dtype != MVR_F16) return MVR_ERR_DTYPE;
+  if (offset_dtype != dtype && !(dtype == MVR_F16 && offset_dtype == MVR_F32)) return MVR_ERR_DTYPE;
   if (order != 0 && order != 1 && order != 3) return MVR_ERR_ORDER;
   if (B < 0 || C < 0 || D < 1 || H < 1 || W < 1) return MVR_ERR_SHAPE;
   if (D * H * W >= 0x7fffffffLL || B > INT32_MAX || C > INT32_MAX) return MVR_ERR_TOO_LARGE;
@@ -252,20 +253,21 @@ static int apply_offset_impl(const void* img, const void* offset, void* out, int
   p.B = (int)B; p.C = (int)C; p.D = (int)D; p.H = (int)H; p.W = (int)W;
   p.order = order;
   p.fm = kReferenceContraction;
-  const size_t pair = (dtype == MVR_F32 ? 4 : 2) * 2;
-  p.vec_ok = ((W & 1) == 0) && ((uintptr_t)offset % pair == 0) && ((uintptr_t)out % pair == 0);
+  p.off_f32 = (dtype == MVR_F16 && offset_dtype == MVR_F32) ? 1 : 0;
+  const size_t pair = (dtype == MVR_F32 ? 4 : 2) * 2, off_pair = (offset_dtype == MVR_F32 ? 4 : 2) * 2;
+  p.vec_ok = ((W & 1) == 0) && ((uintptr_t)offset % off_pair == 0) && ((uintptr_t)out % pair == 0);
   const int rc = ndim == 2 ? launch_apply_offset<2>(p, dtype, (cudaStream_t)stream)
                            : launch_apply_offset<3>(p, dtype, (cudaStream_t)stream);
   return rc == 0 ? MVR_OK : (rc == -9 ? MVR_ERR_TOO_LARGE : MVR_ERR_LAUNCH);
 }
 
-int mvr_apply_offset_2d(const void* img, const void* offset, void* out, int dtype, int64_t B, int64_t C, int64_t H,
-                        int64_t W, int order, void* stream) {
-  return apply_offset_impl(img, offset, out, dtype, 2, B, C, 1, H, W, order, stream);
+int mvr_apply_offset_2d(const void* img, const void* offset, void* out, int dtype, int offset_dtype, int64_t B,
+                        int64_t C, int64_t H, int64_t W, int order, void* stream) {
+  return apply_offset_impl(img, offset, out, dtype, offset_dtype, 2, B, C, 1, H, W, order, stream);
 }
-int mvr_apply_offset_3d(const void* img, const void* offset, void* out, int dtype, int64_t B, int64_t C, int64_t D,
-                        int64_t H, int64_t W, int order, void* stream) {
-  return apply_offset_impl(img, offset, out, dtype, 3, B, C, D, H, W, order, stream);
+int mvr_apply_offset_3d(const void* img, const void* offset, void* out, int dtype, int offset_dtype, int64_t B,
+                        int64_t C, int64_t D, int64_t H, int64_t W, int order, void* stream) {
+  return apply_offset_impl(img, offset, out, dtype, offset_dtype, 3, B, C, D, H, W, order, stream);
 }
 
 // ---- the reference's extension surface --------------------------------------------------

@@ -23,9 +23,30 @@ struct OffsetParams {
   const void* off;   // (B, NDIM, [D,] H, W): displacement along d, h, w (3D) or h, w (2D), in voxels
   void* out;         // (B, C, [D,] H, W)
   int B, C, D, H, W, order, fm, vec_ok;
+  int off_f32;       // the field is float32 although the image is half: rounded to half on load (= offset.half())
 };
 
 constexpr int kOffsetThreads = 256;
+
+// two w-adjacent displacements of one axis, as the image's element type
+template <typename T>
+__device__ __forceinline__ typename P2<T>::V load_offset_pair(const OffsetParams& p, long long q, bool has_b) {
+  typedef P2<T> Q;
+  const T* f = (const T*)p.off + q;
+  if (p.vec_ok) return *reinterpret_cast<const typename Q::V*>(f);
+  return Q::make(f[0], has_b ? f[1] : Ar<T>::fi(0));
+}
+template <>
+__device__ __forceinline__ __half2 load_offset_pair<__half>(const OffsetParams& p, long long q, bool has_b) {
+  if (p.off_f32) {
+    const float* f = (const float*)p.off + q;
+    if (p.vec_ok) return __float22half2_rn(*reinterpret_cast<const float2*>(f));
+    return __floats2half2_rn(f[0], has_b ? f[1] : 0.0f);
+  }
+  const __half* f = (const __half*)p.off + q;
+  if (p.vec_ok) return *reinterpret_cast<const __half2*>(f);
+  return __halves2half2(f[0], has_b ? f[1] : __float2half_rn(0.0f));
+}
 
 template <typename T, int NDIM, bool CUBIC>
 __device__ __forceinline__ void apply_offset_pair(const OffsetParams& p, int b, int d, int h, int wp) {
@@ -36,19 +57,15 @@ __device__ __forceinline__ void apply_offset_pair(const OffsetParams& p, int b, 
   const bool has_b = w0 + 1 < p.W;
   const long long vol = (long long)p.D * p.H * p.W;
   const long long s0 = ((long long)d * p.H + h) * p.W + w0;
-  const T* off = (const T*)p.off + (long long)b * NDIM * vol + s0;
+  const long long off0 = (long long)b * NDIM * vol + s0;
   const T zero = A::fi(0);
 
   // displacement of the two voxels per axis (index 0 = w, 1 = h, 2 = d)
   V o2[3];
 #pragma unroll
   for (int a = 0; a < NDIM; ++a) {
-    const T* q = off + (long long)(NDIM - 1 - a) * vol;  // channel order of the field: d, h, w
-    if (p.vec_ok) {
-      o2[a] = *reinterpret_cast<const V*>(q);
-    } else {
-      o2[a] = Q::make(q[0], has_b ? q[1] : zero);
-    }
+    const long long q = off0 + (long long)(NDIM - 1 - a) * vol;  // channel order of the field: d, h, w
+    o2[a] = load_offset_pair<T>(p, q, has_b);
   }
   // sample positions: (T)index + offset
   const V cx = Q::add(Q::make(A::fi(w0), A::fi(w0 + 1)), o2[0]);

@@ -41,15 +41,11 @@ def affine_3d(features, rois, out_size, spatial_scale, sampling_ratio=0, aligned
 def _apply_offset(ndim, img, offset, order):
     assert img.shape[2:] == offset.shape[2:]
     assert offset.shape[1] == ndim
-    channels = img.shape[1]
-    # signature-compatible call of the extension function (identity weight, zero bias, 1x1 kernel);
-    # neither tensor is read by the kernel, so they are not materialised on the device
-    weight = torch.empty((channels, channels) + (1,) * ndim, device='meta')
-    bias = torch.empty(channels, device='meta')
-    offset = offset.to(device=img.device, dtype=img.dtype)
-    ones, zeros = (1,) * ndim, (0,) * ndim
-    fn = _C.deform_2d if ndim == 2 else _C.deform_3d
-    output = fn(img.contiguous(), weight, bias, offset.contiguous(), *ones, *ones, *zeros, *ones, 1, 1, 64, order)
+    assert img.dim() == ndim + 2
+    offset = offset.to(img.device)
+    if not (img.dtype == torch.float16 and offset.dtype == torch.float32):
+        offset = offset.to(img.dtype)  # a float field under a half image is rounded inside the kernel
+    output = _C.apply_offset(img.contiguous(), offset.contiguous(), order)
     assert img.shape == output.shape, f"input is {img.shape}, out is {output.shape}"
     return output
 

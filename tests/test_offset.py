@@ -191,6 +191,24 @@ def test_kernel_with_unaligned_views_and_empty_batch():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("spatial", [(6, 10, 12), (5, 7, 9), (14, 18)])
+def test_float_field_under_a_half_image_is_rounded_on_load(spatial):
+    """apply_offset_* casts the field to the image's dtype first (cuda_fun_tools.py:116-119); the
+    kernel does that rounding itself when it is handed a float32 field and a half image."""
+    gen = torch.Generator().manual_seed(21)
+    ndim = len(spatial)
+    img = torch.rand((2, 2) + spatial, generator=gen).half().cuda()
+    field = (torch.randn((2, ndim) + spatial, generator=gen) * 2).cuda()
+    for order in (0, 1, 3):
+        fused = _lib_apply(img, field, order)
+        assert torch.equal(fused, _lib_apply(img, field.half(), order))
+    assert n_mismatch(_lib_apply(img, field, 1), port.apply_offset(img, field.half(), 1)) == 0
+    from medvision_b200 import _C
+    with pytest.raises(RuntimeError, match="expected scalar type"):
+        _C.apply_offset(img.float(), field.half(), 1)
+
+
+@pytest.mark.gpu
 def test_full_size_volume_properties():
     """128 x 320 x 320 half volume (the elastic-deformation working size of a CT crop):
     zero field = identity, whole-voxel field = shifted copy, and a smooth random field against
