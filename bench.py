@@ -522,7 +522,7 @@ def main():
                        "l2": "inputs (%.2f GB per GPU) larger than L2, no flush" %
                              (wl["features"].numel() * 2 / 1e9),
                        "sampling_ratio": 1, "order": 1, "aligned": True},
-            "gpu_launches": args.steps, "clocks": clocks}
+            "gpu_launches": 2 * args.steps, "clocks": clocks}
     if args.impl == "reference":
         line["impl"] = "reference"
         line["config"]["device"] = "cuda: the reference's own kernels, compiled unmodified for sm_100a"

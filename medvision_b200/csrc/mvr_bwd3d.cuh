@@ -22,6 +22,16 @@ template <> struct BwdAcc<float> { typedef float type; };
 template <> struct BwdAcc<__half> { typedef float type; };
 
 __device__ __forceinline__ void bwd_red(float* p, float v) { atomicAdd(p, v); }  // result unused: a reduction
+// The two x-neighbours of a tap row are adjacent in memory: when the lower one sits on an 8-byte
+// boundary both go to L2 as one two-element reduction (one operation on one sector instead of two).
+__device__ __forceinline__ void bwd_red_row(float* p0, float* p1, float v0, float v1) {
+  if (p1 == p0 + 1 && (reinterpret_cast<unsigned long long>(p0) & 7ull) == 0) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p0), "f"(v0), "f"(v1) : "memory");
+  } else {
+    atomicAdd(p0, v0);
+    atomicAdd(p1, v1);
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kS3Threads)
@@ -97,11 +107,11 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
       Acc* p0 = acc + e.o0;
       Acc* p1 = acc + e.o1;
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const V gk = Q::mul(g2, w[t]);
+      for (int t = 0; t < 8; t += 2) {
+        const V g0 = Q::mul(g2, w[t]), g1 = Q::mul(g2, w[t + 1]);
         Acc* pl = (t < 4) ? p0 : p1;
-        if (ina) bwd_red(pl + oa[t & 3], A::tof(Q::lo(gk)));
-        if (inb) bwd_red(pl + ob[t & 3], A::tof(Q::hi(gk)));
+        if (ina) bwd_red_row(pl + oa[t & 3], pl + oa[(t & 3) + 1], A::tof(Q::lo(g0)), A::tof(Q::lo(g1)));
+        if (inb) bwd_red_row(pl + ob[t & 3], pl + ob[(t & 3) + 1], A::tof(Q::hi(g0)), A::tof(Q::hi(g1)));
       }
     }
     return;
@@ -127,7 +137,8 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
       long long off[8];
       if (!make_taps<T, 3>(p.D, p.H, p.W, rz[s], ry[s], rx[s], p.order, w, off)) continue;
 #pragma unroll
-      for (int t = 0; t < 8; ++t) bwd_red(acc + off[t], A::tof(A::mul(gv[s], w[t])));
+      for (int t = 0; t < 8; t += 2)
+        bwd_red_row(acc + off[t], acc + off[t + 1], A::tof(A::mul(gv[s], w[t])), A::tof(A::mul(gv[s], w[t + 1])));
     }
   }
   (void)HW;
@@ -171,6 +182,7 @@ inline bool bwd_stream3d_applicable(const Params& p, int dtype, S3Launch& L, lon
   L.chunks = (p.od + chunk - 1) / chunk;
   L.vec_store = 0;
   L.ring_bytes = 0;
+  L.filter = 0;
   ctas = per_depth_ctas * L.chunks;
   return ctas <= 0x7fffffffLL;
 }

@@ -200,6 +200,7 @@ struct S3Launch {
   int tiles_w, tiles_h, chunks, chunk;  // chunk = output depths per CTA
   int vec_store;                        // 1: two-element vector stores are aligned
   int ring_bytes;                       // TMA-staged kernel: bytes of the shared-memory plane ring
+  int filter;                           // 0: every roi; 1: only rois that turn about z at most; 2: only the others
 };
 
 // General-rotation depth loop for NP voxel pairs of one thread (pair q sits q*row_step output
@@ -294,9 +295,8 @@ struct S3Cta {
   int tw, th, ck, c, pd0, npd;
   long long nc, n;
 };
-__device__ __forceinline__ S3Cta s3_cta(const Params& p, const S3Launch& L) {
+__device__ __forceinline__ S3Cta s3_cta(const Params& p, const S3Launch& L, long long cta) {
   S3Cta k;
-  long long cta = blockIdx.x;
   k.tw = (int)(cta % L.tiles_w); cta /= L.tiles_w;
   k.th = (int)(cta % L.tiles_h); cta /= L.tiles_h;
   k.ck = (int)(cta % L.chunks);  cta /= L.chunks;
@@ -306,6 +306,24 @@ __device__ __forceinline__ S3Cta s3_cta(const Params& p, const S3Launch& L) {
   k.pd0 = k.ck * L.chunk;
   k.npd = min(L.chunk, p.od - k.pd0);
   return k;
+}
+__device__ __forceinline__ S3Cta s3_cta(const Params& p, const S3Launch& L) { return s3_cta(p, L, blockIdx.x); }
+
+// The forward runs as two launches when the rois may be rotated: rois that turn about z at most
+// stream whole source planes through shared memory and want few, long CTAs (their set-up costs
+// as much as five depths); rois under a general rotation gather through L1, are bound by load
+// latency and want many short work items.  The test reads the two angles themselves (exact
+// zeros give sin = 0 and cos = 1 exactly), so it needs no decoding and both launches agree.
+template <typename T>
+__device__ __forceinline__ bool s3_roi_is_planar(const Params& p, long long n) {
+  if (p.kind != KIND_ROTATED) return true;
+  const T* r = (const T*)p.rois + n * 10;
+  return (Ar<T>::tof(__ldg(r + 7)) == 0.0f) && (Ar<T>::tof(__ldg(r + 8)) == 0.0f);
+}
+template <typename T>
+__device__ __forceinline__ bool s3_filtered_out(const Params& p, const S3Launch& L, const S3Cta& k) {
+  if (L.filter == 0) return false;
+  return s3_roi_is_planar<T>(p, k.n) != (L.filter == 1);
 }
 
 // Decode the roi, classify it, and fill the per-depth table.  Ends with a __syncthreads().
@@ -504,8 +522,41 @@ __global__ void __launch_bounds__(kS3Threads)
 resample_fwd_stream3d(const Params p, const S3Launch L) {
   __shared__ S3Shared<T> sh;
   const S3Cta k = s3_cta(p, L);
+  if (s3_filtered_out<T>(p, L, k)) return;
   s3_prologue<T>(p, k, sh);
   s3_body_l1<T>(p, L, k, sh);
+}
+
+// The second launch of a rotated forward: the rois under a general rotation, which the
+// plane-streaming launch left out.  A fixed grid of CTAs (a few per SM) first marks those rois
+// in a shared bit mask -- when there is none, which is the usual case for the augmentations, the
+// whole grid is gone after a few loads -- and then strides over the (roi, channel, tile, chunk)
+// work items of the marked rois.
+constexpr int kS3RestMaxRois = 16384;
+template <typename T>
+__global__ void __launch_bounds__(kS3Threads)
+resample_fwd_stream3d_rest(const Params p, const S3Launch L, long long items) {
+  __shared__ S3Shared<T> sh;
+  __shared__ unsigned general[kS3RestMaxRois / 32];
+  // the launch that follows in the stream (the plane-streaming kernel) depends on nothing this
+  // kernel writes: let it start as soon as every CTA of this grid has got here
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  int mine = 0;
+  for (int n0 = 0; n0 < p.R; n0 += kS3Threads) {
+    const int n = n0 + threadIdx.x;
+    const bool g = n < p.R && !s3_roi_is_planar<T>(p, n);
+    const unsigned m = __ballot_sync(0xffffffffu, g);
+    if ((threadIdx.x & 31) == 0 && n < kS3RestMaxRois) general[n >> 5] = m;
+    mine |= g;
+  }
+  if (!__syncthreads_or(mine)) return;
+  for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+    const S3Cta k = s3_cta(p, L, item);
+    if (!((general[k.n >> 5] >> (k.n & 31)) & 1u)) continue;  // CTA-uniform
+    s3_prologue<T>(p, k, sh);
+    s3_body_l1<T>(p, L, k, sh);
+    __syncthreads();  // the next item's prologue overwrites the tables
+  }
 }
 
 }  // namespace mvr

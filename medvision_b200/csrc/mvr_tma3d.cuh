@@ -178,6 +178,7 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
   T3Shared<T>& sh = *reinterpret_cast<T3Shared<T>*>(t3_dyn + L.ring_bytes);
 
   const S3Cta k = s3_cta(p, L);  // k.th counts tiles of 16*NP rows here
+  if (s3_filtered_out<T>(p, L, k)) return;
   if (threadIdx.x == 0) {
     sh.box[0] = 0x7fffffff; sh.box[1] = -0x7fffffff; sh.box[2] = 0x7fffffff; sh.box[3] = -0x7fffffff;
     sh.abort_flag = 0;
@@ -553,44 +554,114 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   const bool tma = use_tma && t3_make_maps(p, dtype, maps);
   static const int env_pairs = getenv("MVR_T3_PAIRS") ? atoi(getenv("MVR_T3_PAIRS")) : 0;
   const int pairs = (env_pairs == 1 || env_pairs == 2) ? env_pairs : kT3Pairs;
-  const int tile_h = tma ? kS3TileH * pairs : kS3TileH;  // output rows per CTA
 
-  S3Launch L;
-  L.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
-  L.tiles_h = (p.oh + tile_h - 1) / tile_h;
-  // depth chunk: long enough to amortise the per-thread set-up and to reuse planes, short
-  // enough to give every SM several CTAs
-  const long long per_depth_ctas = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
-  int chunk = kS3MaxChunk;
-  while (chunk > 8 && per_depth_ctas * ((p.od + chunk - 1) / chunk) < 148LL * 8) chunk >>= 1;
-  if (chunk > p.od) chunk = p.od;
-  L.chunk = chunk;
-  L.chunks = (p.od + chunk - 1) / chunk;
   const size_t esz = dtype == 0 ? 4 : 2;
-  L.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % (2 * esz) == 0);
+  static const int env_chunk = getenv("MVR_T3_CHUNK") ? atoi(getenv("MVR_T3_CHUNK")) : 0;
+  static const int env_ring = getenv("MVR_T3_RING_KB") ? atoi(getenv("MVR_T3_RING_KB")) : 0;
+
+  // ---- geometry of the gather kernel (plain loads through L1): 32 x 16 tiles, short depth chunks.
+  // Rois under a general rotation are bound by load latency and want many CTAs.  Measured on
+  // RandomAffine 16 x 128^3 with three-axis rotations: 8 depths per CTA 329 us, 16: 365, 32: 430,
+  // 64: 725.
+  S3Launch G;
+  G.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
+  G.tiles_h = (p.oh + kS3TileH - 1) / kS3TileH;
+  const long long g_per_depth = (long long)p.R * p.C * G.tiles_w * G.tiles_h;
+  {
+    int chunk = kS3MaxChunk;
+    while (chunk > 8 && g_per_depth * ((p.od + chunk - 1) / chunk) < 148LL * 16) chunk >>= 1;
+    if (env_chunk > 0) chunk = min(env_chunk, kS3MaxChunk);
+    G.chunk = min(chunk, p.od);
+  }
+  G.chunks = (p.od + G.chunk - 1) / G.chunk;
+  G.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % (2 * esz) == 0);
+  G.ring_bytes = 0;
+  G.filter = 0;
+  const long long g_ctas = g_per_depth * G.chunks;
+  if (g_ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
+  if (!tma) {
+    if (dtype == 0) resample_fwd_stream3d<float><<<(unsigned)g_ctas, kS3Threads, 0, st>>>(p, G);
+    else resample_fwd_stream3d<__half><<<(unsigned)g_ctas, kS3Threads, 0, st>>>(p, G);
+    return cudaGetLastError() == cudaSuccess ? 0 : -8;
+  }
+
+  // ---- geometry of the plane-streaming kernel: 32 x 16*pairs tiles, long depth chunks.
+  // The set-up of a CTA costs about as much as five depths, so: the fewest chunks that still give
+  // every SM about five CTAs.  Measured on Resize 4 x (160,512,512) -> (128,256,256): 43 depths
+  // per CTA 83 us, 26: 84, 64: 87, 16: 91; on 96^3 crops one chunk of 96 beats two of 48 by 9 %.
+  S3Launch L;
+  L.tiles_w = G.tiles_w;
+  L.tiles_h = (p.oh + kS3TileH * pairs - 1) / (kS3TileH * pairs);
+  const long long per_depth_ctas = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
+  {
+    long long want = (148LL * 5 + per_depth_ctas - 1) / per_depth_ctas;
+    want = std::max<long long>(want, (p.od + kS3MaxChunk - 1) / kS3MaxChunk);
+    want = std::min<long long>(want, std::max(1, p.od / 8));
+    int chunk = (int)((p.od + want - 1) / want);
+    if (env_chunk > 0) chunk = min(min(env_chunk, kS3MaxChunk), p.od);
+    L.chunk = chunk;
+  }
+  L.chunks = (p.od + L.chunk - 1) / L.chunk;
+  L.vec_store = G.vec_store;
   const long long ctas = per_depth_ctas * L.chunks;
   if (ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
-  // ring of plane boxes: what two (NP = 2) or three (NP = 1) resident CTAs per SM can share
-  static const int env_ring = getenv("MVR_T3_RING_KB") ? atoi(getenv("MVR_T3_RING_KB")) : 0;
+  // ring of plane boxes: what three resident CTAs per SM can share
   L.ring_bytes = (env_ring > 0 ? env_ring : 60) * 1024;
-  if (tma) {
-    // more dynamic shared memory than the default limit: opt in (per function and device)
+  // axis-aligned boxes have no rotation: one launch; rotated rois: this launch takes those that turn
+  // about z at most, the gather launch below takes the rest
+  const bool two = (p.kind == KIND_ROTATED);
+  L.filter = two ? 1 : 0;
+  G.filter = 2;
+  // The gather launch goes first and lets its dependents start as soon as its CTAs are resident
+  // (programmatic dependent launch); the plane-streaming launch is that dependent and waits for
+  // nothing, since the two write disjoint rois.  When no roi is under a general rotation the
+  // gather CTAs are gone after a few loads and the two launches cost one kernel boundary, not two.
+  bool overlap = false;
+  if (two) {
+    if (p.R <= kS3RestMaxRois) {
+      static int occ[2] = {0, 0};  // resident CTAs per SM of the two instantiations
+      if (occ[dtype] == 0) {
+        int n = 0;
+        if (dtype == 0) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, resample_fwd_stream3d_rest<float>, kS3Threads, 0);
+        else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, resample_fwd_stream3d_rest<__half>, kS3Threads, 0);
+        occ[dtype] = n > 0 ? n : 1;
+      }
+      const unsigned grid = (unsigned)std::min<long long>(g_ctas, 148LL * occ[dtype]);
+      G.filter = 0;
+      if (dtype == 0) resample_fwd_stream3d_rest<float><<<grid, kS3Threads, 0, st>>>(p, G, g_ctas);
+      else resample_fwd_stream3d_rest<__half><<<grid, kS3Threads, 0, st>>>(p, G, g_ctas);
+      overlap = true;
+    } else {
+      if (dtype == 0) resample_fwd_stream3d<float><<<(unsigned)g_ctas, kS3Threads, 0, st>>>(p, G);
+      else resample_fwd_stream3d<__half><<<(unsigned)g_ctas, kS3Threads, 0, st>>>(p, G);
+    }
+    if (cudaGetLastError() != cudaSuccess) return -8;
+  }
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3(kT3Threads);
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;
+  cudaError_t err = cudaSuccess;
+  // more dynamic shared memory than the default limit: opt in (per function and device)
 #define T3_LAUNCH(TYPE, NP)                                                                                  \
   {                                                                                                          \
+    cfg.dynamicSmemBytes = t3_dynamic_smem<TYPE>(L.ring_bytes);                                              \
     cudaFuncSetAttribute(resample_fwd_stream3d_tma<TYPE, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                         (int)t3_dynamic_smem<TYPE>(L.ring_bytes));                                          \
-    resample_fwd_stream3d_tma<TYPE, NP><<<(unsigned)ctas, kT3Threads, t3_dynamic_smem<TYPE>(L.ring_bytes), st>>>(p, L, maps); \
+                         (int)cfg.dynamicSmemBytes);                                                         \
+    err = cudaLaunchKernelEx(&cfg, resample_fwd_stream3d_tma<TYPE, NP>, p, L, maps);                         \
   }
-    if (dtype == 0) {
-      if (pairs == 2) T3_LAUNCH(float, 2) else T3_LAUNCH(float, 1)
-    } else {
-      if (pairs == 2) T3_LAUNCH(__half, 2) else T3_LAUNCH(__half, 1)
-    }
-#undef T3_LAUNCH
+  if (dtype == 0) {
+    if (pairs == 2) T3_LAUNCH(float, 2) else T3_LAUNCH(float, 1)
   } else {
-    if (dtype == 0) resample_fwd_stream3d<float><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
-    else resample_fwd_stream3d<__half><<<(unsigned)ctas, kS3Threads, 0, st>>>(p, L);
+    if (pairs == 2) T3_LAUNCH(__half, 2) else T3_LAUNCH(__half, 1)
   }
+#undef T3_LAUNCH
+  if (err != cudaSuccess) return -8;
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
