@@ -351,7 +351,33 @@ def detection_configs(impl_name):
             res.append({"workload": name, "pass": "fwd+bwd" if bwd else "fwd", "us_per_call": ms * 1e3,
                         "gvoxel_per_s": n_out / (ms * 1e-3) / 1e9, "note": "latency-bound; includes autograd and Python"})
 
+    def run_graph(name, fwd_name, bwd_name, feat, rois, out_size, extra):
+        """The two extension calls alone, replayed from a CUDA graph: launch and Python overhead removed."""
+        from medvision_b200 import _C
+        feat = feat.cuda()
+        rois = rois.cuda().to(feat.dtype)
+        out = torch.empty((rois.size(0), feat.size(1)) + tuple(out_size), dtype=feat.dtype, device="cuda")
+        grad = torch.randn_like(out)
+        gin = torch.zeros_like(feat)
+        calls = {"fwd": lambda: getattr(_C, fwd_name)(feat, rois, out, *out_size, 1.0, 2, *extra, 1),
+                 "bwd": lambda: getattr(_C, bwd_name)(grad, rois, gin, *out_size, 1.0, 2, *extra, 1)}
+        for key, call in calls.items():
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                call()  # first call outside the capture (lazy set-up)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        call()
+            torch.cuda.synchronize()
+            ms = time_steps(graph.replay, 20, 5, 1) / (20 * 20)
+            res.append({"workload": name, "pass": key + " kernel, CUDA-graph replay", "us_per_call": ms * 1e3,
+                        "gvoxel_per_s": out.numel() / (ms * 1e-3) / 1e9})
+
     feat, rois = config1_inputs()
+    run_graph("RoIAlign 3D fp32 (2,4,64,64,64), 128 rois, 7x7x7, sampling_ratio 2", "roi_align_3d_forward",
+              "roi_align_3d_backward", feat, rois, (7, 7, 7), ())
     run("RoIAlign 3D fp32 (2,4,64,64,64), 128 rois, 7x7x7, sampling_ratio 2",
         RoIAlign((7, 7, 7), 1.0, 2), feat, rois, 128 * 4 * 343)
     g = torch.Generator().manual_seed(2)
@@ -362,6 +388,8 @@ def detection_configs(impl_name):
                         (torch.rand(512, 1, generator=g) * 2 - 1) * math.pi], 1)
         run("RoIAlignRotated 2D %s (8,3,512,512), 512 rois, 14x14, sampling_ratio 2" % str(dt)[6:],
             RoIAlignRotated((14, 14), 1.0, 2), f2, r2, 512 * 3 * 196)
+        run_graph("RoIAlignRotated 2D %s (8,3,512,512), 512 rois, 14x14, sampling_ratio 2" % str(dt)[6:],
+                  "roi_align_rotated_2d_forward", "roi_align_rotated_2d_backward", f2, r2, (14, 14), (True,))
     return res
 
 

@@ -54,7 +54,8 @@ def _check(op, data, rois, other, size_rois):
         raise RuntimeError(f"{op} is not implemented on CPU")
     if rois.dim() != 2 or rois.size(1) != size_rois:
         raise RuntimeError(f"wrong roi size! size_rois should be {size_rois}")
-    if not (rois.is_cuda and other.is_cuda) or rois.device != data.device or other.device != data.device:
+    dev = data.device
+    if rois.device != dev or other.device != dev:
         raise RuntimeError("expected all tensors to be on the same CUDA device")
     if rois.dtype != data.dtype or other.dtype != data.dtype:
         # the reference reinterprets with tensor.data<scalar_t>(), which throws on a mismatch
@@ -67,33 +68,51 @@ def _call(fn, *args):
         raise RuntimeError(_lib.strerror(rc))
 
 
+_FN = {name: getattr(_lib.lib, name) for name in _lib.PROTOTYPES}
+_raw_stream = torch._C._cuda_getCurrentRawStream  # (device index) -> cudaStream_t of torch's current stream
+_current_device = torch._C._cuda_getDevice
+
+
+def _launch(fn, device, args):
+    """Call ``fn(*args, stream)`` with ``device`` current and torch's current stream of that device."""
+    index = device.index
+    if _current_device() == index:
+        rc = fn(*args, _raw_stream(index))
+    else:
+        with torch.cuda.device(index):
+            rc = fn(*args, _raw_stream(index))
+    if rc != 0:
+        raise RuntimeError(_lib.strerror(rc))
+
+
 def _run(name, op, ndim, kind_width, a, rois, b, out_sizes, spatial_scale, sampling_ratio, aligned, order, forward):
     """a: features (fwd) or top_grad (bwd); b: output (fwd) or bottom_grad (bwd)."""
     feat = a if forward else b
     _check(op, a, rois, b, kind_width)
-    code = _dtype_code(a, name)
+    code = _DTYPES.get(a.dtype)
+    if code is None:
+        _dtype_code(a, name)
     if feat.dim() != ndim + 2:
         raise RuntimeError(f"{name}: expected a {ndim + 2}-D feature tensor")
-    a_c = a.contiguous()
-    rois_c = rois.contiguous()
+    if not a.is_contiguous():
+        a = a.contiguous()
+    if not rois.is_contiguous():
+        rois = rois.contiguous()
     if not b.is_contiguous():
         raise RuntimeError(f"{name}: the result tensor must be contiguous")
-    N, C = feat.size(0), feat.size(1)
-    spatial = list(feat.shape[2:])
-    R = rois.size(0)
-    expect = (R, C) + tuple(out_sizes)
+    fshape = feat.shape
+    R = rois.shape[0]
     other = b if forward else a
-    if tuple(other.shape) != expect:
-        raise RuntimeError(f"{name}: expected a tensor of shape {expect}, got {tuple(other.shape)}")
-    fn = getattr(_lib.lib, "mvr_" + name)
-    with torch.cuda.device(a.device):
-        stream = torch.cuda.current_stream(a.device).cuda_stream
-        args = [a_c.data_ptr(), rois_c.data_ptr(), b.data_ptr(), code, N, C] + spatial + [R, rois.size(1)] + \
-               list(out_sizes) + [float(spatial_scale), int(sampling_ratio)]
-        if aligned is not None:
-            args.append(int(bool(aligned)))
-        args += [int(order), _status_ptr(a.device), stream]
-        _call(fn, *args)
+    if other.shape != (R, fshape[1], *out_sizes):
+        raise RuntimeError(f"{name}: expected a tensor of shape {(R, fshape[1], *out_sizes)}, got {tuple(other.shape)}")
+    device = a.device
+    if aligned is None:
+        args = (a.data_ptr(), rois.data_ptr(), b.data_ptr(), code, *fshape, R, kind_width, *out_sizes,
+                float(spatial_scale), int(sampling_ratio), int(order), _status_ptr(device))
+    else:
+        args = (a.data_ptr(), rois.data_ptr(), b.data_ptr(), code, *fshape, R, kind_width, *out_sizes,
+                float(spatial_scale), int(sampling_ratio), 1 if aligned else 0, int(order), _status_ptr(device))
+    _launch(_FN["mvr_" + name], device, args)
 
 
 def roi_align_2d_forward(input, rois, output, aligned_height, aligned_width, spatial_scale, sampling_ratio, order):
@@ -175,11 +194,9 @@ def apply_offset(input, offset, order):
     assert input.is_contiguous(), "input tensor has to be contiguous"
     offset = offset.contiguous()
     out = torch.empty_like(input)
-    fn = getattr(_lib.lib, "mvr_apply_offset_%dd" % ndim)
-    with torch.cuda.device(input.device):
-        stream = torch.cuda.current_stream(input.device).cuda_stream
-        _call(fn, input.data_ptr(), offset.data_ptr(), out.data_ptr(), _DTYPES[input.dtype], _DTYPES[offset.dtype],
-              input.size(0), input.size(1), *input.shape[2:], int(order), stream)
+    _launch(_FN["mvr_apply_offset_%dd" % ndim], input.device,
+            (input.data_ptr(), offset.data_ptr(), out.data_ptr(), _DTYPES[input.dtype], _DTYPES[offset.dtype],
+             *input.shape, int(order)))
     return out
 
 

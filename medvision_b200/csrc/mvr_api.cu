@@ -11,6 +11,7 @@
 #include "mvr_bwd3d.cuh"
 #include "mvr_offset.cuh"
 #include "mvr_cubic3d.cuh"
+#include "mvr_flat.cuh"
 
 // ---- scratch of the entry point that allocates nothing ------------------------------------
 // Lives in the library image: every GPU that loads the library holds these 16 MiB until the
@@ -123,6 +124,15 @@ int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
       default: rc = launch_cubic3d<double>(p, st); break;
     }
     if (rc < 0) return MVR_ERR_TOO_LARGE;
+    if (rc == 0) return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
+  }
+  {
+    int rc;
+    switch (dtype) {
+      case MVR_F32: rc = launch_flat<float>(p, fwd, st); break;
+      case MVR_F16: rc = launch_flat<__half>(p, fwd, st); break;
+      default: rc = launch_flat<double>(p, fwd, st); break;
+    }
     if (rc == 0) return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
   }
   switch (dtype) {

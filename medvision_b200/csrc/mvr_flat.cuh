@@ -1,0 +1,158 @@
+// Forward and backward for the calls the streaming kernels do not take (detection heads: many
+// small rois, a few output bins each, several samples per bin; 2D; double; sampling_ratio != 1),
+// orders 0 and 1.
+//
+// Work is laid out flat, as in the reference (one thread per output element in (roi, channel,
+// [d,] h, w) order), so every thread of a CTA has work whatever the size of a roi's output.  What
+// differs from the reference (medvision/csrc/cuda/roi_align_rotated_3d_cuda_kernel.cuh:15-120 and
+// siblings): the rois a CTA's 256 outputs belong to (at most kFlatMaxRois) are decoded once each,
+// by different threads at the same time, into shared memory -- the reference decodes the roi and
+// evaluates up to six sin/cos in every thread, and rebuilds the rotation matrix for every sample;
+// the sample loops of the common fixed sampling ratios (1, 2) are unrolled so that all tap loads
+// of an output are in flight together; offsets are 64-bit.  The arithmetic of every sample is
+// the reference's, operation by operation.
+#pragma once
+#include "mvr_generic.cuh"
+
+namespace mvr {
+
+constexpr int kFlatThreads = 256;
+constexpr int kFlatMinPerRoi = 32;                                     // outputs per roi (C * ovol) at least
+constexpr int kFlatMaxRois = kFlatThreads / kFlatMinPerRoi + 2;        // rois a CTA can span
+
+// SR: compile-time sampling ratio per axis (1 or 2), or 0 = taken from the roi at run time
+// (any fixed ratio, or the adaptive ceil(bin) grid).
+// OFF: type of the tap offsets inside one channel's volume (int when D*H*W < 2^31).
+template <typename T, int NDIM, int SR, bool BWD, typename OFF>
+__global__ void __launch_bounds__(kFlatThreads)
+resample_flat(const Params p, int per_roi) {
+  typedef Ar<T> A;
+  __shared__ RoiGeom<T> geo[kFlatMaxRois];
+  const long long total = (long long)p.R * per_roi;
+  const long long e0 = (long long)blockIdx.x * kFlatThreads;
+  const long long n0 = e0 / per_roi;
+  const int rem0 = (int)(e0 - n0 * per_roi);
+  const long long e_last = min(e0 + kFlatThreads, total) - 1;
+  const int n_rois = (int)(e_last / per_roi - n0) + 1;
+  if ((int)threadIdx.x < n_rois) {
+    const int osz[3] = {p.ow, p.oh, p.od};
+    decode_roi<T>((const T*)p.rois, n0 + threadIdx.x, NDIM, p.kind, osz, p.spatial_scale, p.sampling_ratio, p.aligned,
+                  p.fm, geo[threadIdx.x]);
+  }
+  __syncthreads();
+  const long long e = e0 + threadIdx.x;
+  if (e >= total) return;
+  const int t = rem0 + (int)threadIdx.x;
+  const int r = t / per_roi;
+  const int rem = t - r * per_roi;
+  const RoiGeom<T>& g = geo[r];
+  const int ovol = (int)p.ovol;
+  const int c = rem / ovol;
+  const int v = rem - c * ovol;
+  const int pw = v % p.ow;
+  const int ph = (v / p.ow) % p.oh;
+  const int pd = (NDIM == 3) ? v / (p.ow * p.oh) : 0;
+  const T zero = A::fi(0);
+
+  if (g.batch < 0 || g.batch >= p.N) {
+    if (p.status && rem == 0) atomicOr(p.status, STATUS_BAD_BATCH_INDEX);
+    if (!BWD) ((T*)p.out)[e] = zero;
+    return;
+  }
+  // fwd: the volume read; bwd: the gradient volume accumulated into
+  const T* vol = (const T*)(BWD ? p.out : p.in) + ((long long)g.batch * p.C + c) * p.vol;
+  T* gvol = (T*)p.out + ((long long)g.batch * p.C + c) * p.vol;
+  const T go = BWD ? ((const T*)p.in)[e] : zero;
+
+  const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], p.fm);
+  const T by = lattice_base<T>(g.start[1], ph, g.bin[1], p.fm);
+  const T bz = (NDIM == 3) ? lattice_base<T>(g.start[2], pd, g.bin[2], p.fm) : zero;
+  const int gx = SR ? SR : g.grid[0], gy = SR ? SR : g.grid[1], gz = (NDIM == 3) ? (SR ? SR : g.grid[2]) : 1;
+
+  T acc = zero;
+  auto sample = [&](T x, T y, T z) {
+    T sx, sy, sz;
+    to_volume<T, NDIM>(g, p.kind, p.fm, x, y, z, sx, sy, sz);
+    T w[1 << NDIM];
+    OFF off[1 << NDIM];
+    const bool in = make_taps<T, NDIM, OFF>(p.D, p.H, p.W, sz, sy, sx, p.order, w, off);
+    if (BWD) {
+      if (!in) return;
+#pragma unroll
+      for (int k = 0; k < (1 << NDIM); ++k) atomic_add_T(gvol + off[k], A::div(A::mul(go, w[k]), g.count_bwd));
+    } else {
+      T val = zero;
+      if (in) {
+        T tap[1 << NDIM];
+#pragma unroll
+        for (int k = 0; k < (1 << NDIM); ++k) tap[k] = __ldg(vol + off[k]);
+        val = tap_sum<T, (1 << NDIM)>(w, tap, p.fm);
+      }
+      acc = A::add(acc, val);
+    }
+  };
+
+  if (SR) {
+    constexpr int S = SR ? SR : 1;
+    T subx[S], suby[S], subz[S];
+#pragma unroll
+    for (int i = 0; i < S; ++i) {
+      subx[i] = lattice_sub<T>(g.bin[0], i, S);
+      suby[i] = lattice_sub<T>(g.bin[1], i, S);
+      subz[i] = (NDIM == 3) ? lattice_sub<T>(g.bin[2], i, S) : zero;
+    }
+#pragma unroll
+    for (int iz = 0; iz < ((NDIM == 3) ? S : 1); ++iz) {
+      const T z = (NDIM == 3) ? A::add(bz, subz[iz]) : zero;
+#pragma unroll
+      for (int iy = 0; iy < S; ++iy) {
+        const T y = A::add(by, suby[iy]);
+#pragma unroll
+        for (int ix = 0; ix < S; ++ix) sample(A::add(bx, subx[ix]), y, z);
+      }
+    }
+  } else {
+    for (int iz = 0; iz < gz; ++iz) {
+      const T z = (NDIM == 3) ? A::add(bz, lattice_sub<T>(g.bin[2], iz, gz)) : zero;
+      for (int iy = 0; iy < gy; ++iy) {
+        const T y = A::add(by, lattice_sub<T>(g.bin[1], iy, gy));
+        for (int ix = 0; ix < gx; ++ix) sample(A::add(bx, lattice_sub<T>(g.bin[0], ix, gx)), y, z);
+      }
+    }
+  }
+  if (!BWD) ((T*)p.out)[e] = A::div(acc, g.count_fwd);
+}
+
+// 0 launched, 1 not applicable
+template <typename T>
+inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
+  if (p.order > 1) return 1;
+  const long long per_roi = (long long)p.C * p.ovol;
+  if (per_roi < kFlatMinPerRoi || per_roi > (1LL << 30)) return 1;
+  const long long total = (long long)p.R * per_roi;
+  const long long ctas = (total + kFlatThreads - 1) / kFlatThreads;
+  if (ctas > 0x7fffffffLL) return 1;
+  const unsigned grid = (unsigned)ctas;
+  const int pr = (int)per_roi;
+  const int sr = (p.sampling_ratio == 1 || p.sampling_ratio == 2) ? p.sampling_ratio : 0;
+  const bool small = p.vol < 0x7fffffffLL;
+#define MVR_FLAT(ND, SRV)                                                                            \
+  {                                                                                                  \
+    if (small) {                                                                                     \
+      if (fwd) resample_flat<T, ND, SRV, false, int><<<grid, kFlatThreads, 0, st>>>(p, pr);          \
+      else resample_flat<T, ND, SRV, true, int><<<grid, kFlatThreads, 0, st>>>(p, pr);               \
+    } else {                                                                                         \
+      if (fwd) resample_flat<T, ND, SRV, false, long long><<<grid, kFlatThreads, 0, st>>>(p, pr);    \
+      else resample_flat<T, ND, SRV, true, long long><<<grid, kFlatThreads, 0, st>>>(p, pr);         \
+    }                                                                                                \
+  }
+  if (p.ndim == 2) {
+    if (sr == 1) MVR_FLAT(2, 1) else if (sr == 2) MVR_FLAT(2, 2) else MVR_FLAT(2, 0)
+  } else {
+    if (sr == 1) MVR_FLAT(3, 1) else if (sr == 2) MVR_FLAT(3, 2) else MVR_FLAT(3, 0)
+  }
+#undef MVR_FLAT
+  return 0;
+}
+
+}  // namespace mvr

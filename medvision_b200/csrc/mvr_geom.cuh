@@ -214,8 +214,9 @@ __device__ __forceinline__ void nearest_pick(const AxisTap<T>* t, int ndim, T* w
 // Weights and flat element offsets of the 2^ndim taps of a sample at (z, y, x).
 // Returns false when the sample lies outside the [-1, size] band: value 0, no gradient.
 // Tap order: k bit0 = x1, bit1 = y1, bit2 = z1 (the reference's w1..w8 / v1..v8 order).
-template <typename T, int NDIM>
-__device__ __forceinline__ bool make_taps(int D, int H, int W, T z, T y, T x, int order, T* w, long long* off) {
+// OFF = long long, or int when D*H*W < 2^31.
+template <typename T, int NDIM, typename OFF = long long>
+__device__ __forceinline__ bool make_taps(int D, int H, int W, T z, T y, T x, int order, T* w, OFF* off) {
   typedef Ar<T> A;
   AxisTap<T> t[3];
   if (axis_outside<T>(y, H) || axis_outside<T>(x, W)) return false;
@@ -224,10 +225,11 @@ __device__ __forceinline__ bool make_taps(int D, int H, int W, T z, T y, T x, in
   axis_tap<T>(y, H, t[1]);
   if (NDIM == 3) axis_tap<T>(z, D, t[2]);
   if (NDIM == 2) {
-    off[0] = (long long)t[1].i0 * W + t[0].i0;
-    off[1] = (long long)t[1].i0 * W + t[0].i1;
-    off[2] = (long long)t[1].i1 * W + t[0].i0;
-    off[3] = (long long)t[1].i1 * W + t[0].i1;
+    const OFF y0 = (OFF)t[1].i0 * W, y1 = (OFF)t[1].i1 * W;
+    off[0] = y0 + t[0].i0;
+    off[1] = y0 + t[0].i1;
+    off[2] = y1 + t[0].i0;
+    off[3] = y1 + t[0].i1;
     if (order == 0) {
       nearest_pick<T>(t, 2, w);
     } else {
@@ -237,9 +239,9 @@ __device__ __forceinline__ bool make_taps(int D, int H, int W, T z, T y, T x, in
       w[3] = A::mul(t[1].l, t[0].l);
     }
   } else {
-    const long long HW = (long long)H * W;
-    const long long z0 = t[2].i0 * HW, z1 = t[2].i1 * HW;
-    const long long y0 = (long long)t[1].i0 * W, y1 = (long long)t[1].i1 * W;
+    const OFF HW = (OFF)H * W;
+    const OFF z0 = t[2].i0 * HW, z1 = t[2].i1 * HW;
+    const OFF y0 = (OFF)t[1].i0 * W, y1 = (OFF)t[1].i1 * W;
     off[0] = z0 + y0 + t[0].i0;
     off[1] = z0 + y0 + t[0].i1;
     off[2] = z0 + y1 + t[0].i0;
