@@ -13,6 +13,7 @@
 // the reference's, operation by operation.
 #pragma once
 #include "mvr_generic.cuh"
+#include "mvr_stream3d.cuh"
 
 namespace mvr {
 
@@ -123,6 +124,117 @@ resample_flat(const Params p, int per_roi) {
   if (!BWD) ((T*)p.out)[e] = A::div(acc, g.count_fwd);
 }
 
+// Forward for axis-aligned boxes (RoIAlign) with a fixed sampling ratio of 1 or 2.  Without a
+// rotation the sample lattice is a product of three per-axis lattices: the taps and weights of
+// an axis are formed once per axis sample (SR per axis) instead of once per sample (SR^NDIM),
+// and the z*y weight products once per (z, y) sample pair.  Every product and sum is the one the
+// reference forms (w = (hz*hy)*hx, left-to-right tap sum); nearest picks per axis, which selects
+// the same tap as the reference's joint first-match rule.
+template <typename T, int NDIM, int SR, typename OFF>
+__global__ void __launch_bounds__(kFlatThreads, 5)
+resample_flat_box_fwd(const Params p, int per_roi) {
+  typedef Ar<T> A;
+  __shared__ RoiGeom<T> geo[kFlatMaxRois];
+  const long long total = (long long)p.R * per_roi;
+  const long long e0 = (long long)blockIdx.x * kFlatThreads;
+  const long long n0 = e0 / per_roi;
+  const int rem0 = (int)(e0 - n0 * per_roi);
+  const long long e_last = min(e0 + kFlatThreads, total) - 1;
+  const int n_rois = (int)(e_last / per_roi - n0) + 1;
+  if ((int)threadIdx.x < n_rois) {
+    const int osz[3] = {p.ow, p.oh, p.od};
+    decode_roi<T>((const T*)p.rois, n0 + threadIdx.x, NDIM, KIND_BOX, osz, p.spatial_scale, SR, p.aligned, p.fm,
+                  geo[threadIdx.x]);
+  }
+  __syncthreads();
+  const long long e = e0 + threadIdx.x;
+  if (e >= total) return;
+  const int t = rem0 + (int)threadIdx.x;
+  const int r = t / per_roi;
+  const int rem = t - r * per_roi;
+  const RoiGeom<T>& g = geo[r];
+  const int ovol = (int)p.ovol;
+  const int c = rem / ovol;
+  const int v = rem - c * ovol;
+  const int pos[3] = {v % p.ow, (v / p.ow) % p.oh, (NDIM == 3) ? v / (p.ow * p.oh) : 0};
+  const T zero = A::fi(0);
+  if (g.batch < 0 || g.batch >= p.N) {
+    if (p.status && rem == 0) atomicOr(p.status, STATUS_BAD_BATCH_INDEX);
+    ((T*)p.out)[e] = zero;
+    return;
+  }
+  const T* vol = (const T*)p.in + ((long long)g.batch * p.C + c) * p.vol;
+  const int size[3] = {p.W, p.H, p.D};
+  const OFF stride[3] = {(OFF)1, (OFF)p.W, (OFF)p.H * p.W};
+
+  // per axis and axis sample: the two tap offsets, the two weights, and whether the sample counts
+  OFF o0[NDIM][SR], o1[NDIM][SR];
+  T wl[NDIM][SR], wh[NDIM][SR];
+  bool in[NDIM][SR];
+#pragma unroll
+  for (int a = 0; a < NDIM; ++a) {
+    const T base = lattice_base<T>(g.start[a], pos[a], g.bin[a], p.fm);
+#pragma unroll
+    for (int i = 0; i < SR; ++i) {
+      const T cc = A::add(base, lattice_sub<T>(g.bin[a], i, SR));
+      in[a][i] = !axis_outside<T>(cc, size[a]);
+      AxisTap<T> tp;
+      axis_tap<T>(cc, size[a], tp);
+      if (p.order == 0) nearest_axis<T>(tp.l, tp.h);
+      o0[a][i] = tp.i0 * stride[a];
+      o1[a][i] = tp.i1 * stride[a];
+      wl[a][i] = tp.l;
+      wh[a][i] = tp.h;
+    }
+  }
+
+  T acc = zero;
+  if (NDIM == 3) {
+#pragma unroll
+    for (int iz = 0; iz < SR; ++iz) {
+#pragma unroll
+      for (int iy = 0; iy < SR; ++iy) {
+        const T hzhy = A::mul(wh[2][iz], wh[1][iy]), hzly = A::mul(wh[2][iz], wl[1][iy]);
+        const T lzhy = A::mul(wl[2][iz], wh[1][iy]), lzly = A::mul(wl[2][iz], wl[1][iy]);
+        const OFF b00 = o0[2][iz] + o0[1][iy], b01 = o0[2][iz] + o1[1][iy];
+        const OFF b10 = o1[2][iz] + o0[1][iy], b11 = o1[2][iz] + o1[1][iy];
+        const bool in_zy = in[2][iz] && in[1][iy];
+#pragma unroll
+        for (int ix = 0; ix < SR; ++ix) {
+          // the taps of a sample outside the band are still valid addresses (clamped): load and
+          // compute without a branch, then drop the value
+          const OFF x0 = o0[0][ix], x1 = o1[0][ix];
+          const T hx = wh[0][ix], lx = wl[0][ix];
+          const T w[8] = {A::mul(hzhy, hx), A::mul(hzhy, lx), A::mul(hzly, hx), A::mul(hzly, lx),
+                          A::mul(lzhy, hx), A::mul(lzhy, lx), A::mul(lzly, hx), A::mul(lzly, lx)};
+          const T tap[8] = {__ldg(vol + (b00 + x0)), __ldg(vol + (b00 + x1)), __ldg(vol + (b01 + x0)),
+                            __ldg(vol + (b01 + x1)), __ldg(vol + (b10 + x0)), __ldg(vol + (b10 + x1)),
+                            __ldg(vol + (b11 + x0)), __ldg(vol + (b11 + x1))};
+          const T sum = tap_sum<T, 8>(w, tap, p.fm);
+          const T val = (in_zy && in[0][ix]) ? sum : zero;
+          acc = A::add(acc, val);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int iy = 0; iy < SR; ++iy) {
+#pragma unroll
+      for (int ix = 0; ix < SR; ++ix) {
+        const OFF x0 = o0[0][ix], x1 = o1[0][ix], y0 = o0[1][iy], y1 = o1[1][iy];
+        const T w[4] = {A::mul(wh[1][iy], wh[0][ix]), A::mul(wh[1][iy], wl[0][ix]),
+                        A::mul(wl[1][iy], wh[0][ix]), A::mul(wl[1][iy], wl[0][ix])};
+        const T tap[4] = {__ldg(vol + (y0 + x0)), __ldg(vol + (y0 + x1)), __ldg(vol + (y1 + x0)),
+                          __ldg(vol + (y1 + x1))};
+        const T sum = tap_sum<T, 4>(w, tap, p.fm);
+        const T val = (in[1][iy] && in[0][ix]) ? sum : zero;
+        acc = A::add(acc, val);
+      }
+    }
+  }
+  ((T*)p.out)[e] = A::div(acc, g.count_fwd);
+}
+
 // 0 launched, 1 not applicable
 template <typename T>
 inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
@@ -136,6 +248,20 @@ inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
   const int pr = (int)per_roi;
   const int sr = (p.sampling_ratio == 1 || p.sampling_ratio == 2) ? p.sampling_ratio : 0;
   const bool small = p.vol < 0x7fffffffLL;
+  if (fwd && p.kind == KIND_BOX && sr > 0) {
+#define MVR_BOX(ND, SRV)                                                                             \
+  {                                                                                                  \
+    if (small) resample_flat_box_fwd<T, ND, SRV, int><<<grid, kFlatThreads, 0, st>>>(p, pr);         \
+    else resample_flat_box_fwd<T, ND, SRV, long long><<<grid, kFlatThreads, 0, st>>>(p, pr);         \
+  }
+    if (p.ndim == 2) {
+      if (sr == 1) MVR_BOX(2, 1) else MVR_BOX(2, 2)
+    } else {
+      if (sr == 1) MVR_BOX(3, 1) else MVR_BOX(3, 2)
+    }
+#undef MVR_BOX
+    return 0;
+  }
 #define MVR_FLAT(ND, SRV)                                                                            \
   {                                                                                                  \
     if (small) {                                                                                     \
