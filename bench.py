@@ -130,6 +130,10 @@ class Ours:
         from medvision_b200.ops import apply_offset_3d
         return apply_offset_3d(img, field, order)
 
+    def label_forward(self, seg, rois, out_size):
+        from medvision_b200.ops import affine_label_3d
+        return affine_label_3d(seg, rois, tuple(out_size))
+
     def host_forward(self, feat_h, rois_h, out_size, order, out_h):
         """host tensors in, host tensor out: the library's pipelined entry point"""
         from medvision_b200.ops import affine_from_host
@@ -158,6 +162,10 @@ class ReferenceCuda:
     def apply_offset(self, img, field, order):
         from oracle import ref
         return ref.apply_offset(img, field, order)
+
+    def label_forward(self, seg, rois, out_size):
+        """apply_to_seg of the reference's transforms (medvision/aug_cuda_batch/aug_spatial.py:158-194)"""
+        return self.public_forward(seg.float(), rois, out_size, 0).int()
 
 
 # ----------------------------------------------------------------------------- measurement
@@ -426,6 +434,24 @@ def elastic_config(impl, peak):
     return res
 
 
+def label_config(impl, peak):
+    """The segmentation twin of the crop workload on a quarter of its size: 2 int32 label volumes
+    (1,256,512,512), 128 rotated 96^3 patches, nearest, int32 result."""
+    wl = workload_c5("cuda", 0, small=True)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    seg = torch.randint(0, 6, tuple(wl["features"].shape), generator=g, device="cuda", dtype=torch.int32)
+    rois = wl["rois"].float().cuda()
+    out = impl.label_forward(seg, rois, wl["out_size"])
+    ms = time_steps(lambda: impl.label_forward(seg, rois, wl["out_size"]), 20, 5, 1) / 20
+    n = out.numel()
+    U = touched_elements(wl["features"], wl["rois"].to(wl["features"].dtype).cuda(), wl["out_size"], 1)
+    alg = 4 * n + 4 * U  # int32 result written once; at most the linear path's footprint read once
+    return [{"workload": "label crops: 2x(1,256,512,512) int32 -> (128,1,96,96,96) int32, nearest", "pass": "fwd",
+             "ms_per_step": ms, "gvoxel_per_s": n / (ms * 1e-3) / 1e9, "algorithmic_bytes": alg,
+             "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac_of_peak": alg / (ms * 1e-3) / 1e9 / peak,
+             "note": "public call; the reference arm runs seg.float() -> affine_3d(order 0) -> .int()"}]
+
+
 def cpu_baseline_scipy():
     """What the reference's numpy augmentations call for the same job
     (medvision/aug_cpu/aug_spatial.py:475 rotate, :99 zoom), single-threaded scipy."""
@@ -529,7 +555,8 @@ def main():
     impl = Ours() if args.impl == "ours" else ReferenceCuda()
     if args.workload == "elastic":
         if rank == 0:
-            print(json.dumps({"impl": args.impl, "elastic": elastic_config(impl, load_peaks()[0])}))
+            print(json.dumps({"impl": args.impl, "elastic": elastic_config(impl, load_peaks()[0]),
+                              "label": label_config(impl, load_peaks()[0])}))
         return
     sampler = ClockSampler(local)
     if rank == 0:
@@ -601,6 +628,7 @@ def main():
                               "achieved_gbs": b2 / (m2 * 1e-3) / 1e9, "frac_of_peak": b2 / (m2 * 1e-3) / 1e9 / peak,
                               "note": "input fits in L2" if key == "c4" else "input larger than L2"})
             extra += elastic_config(impl, peak)
+            extra += label_config(impl, peak)
             det = detection_configs(args.impl)
             if det:
                 extra += det

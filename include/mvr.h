@@ -58,6 +58,13 @@ extern "C" {
 #define MVR_ERR_NO_DEVICE (-10)
 #define MVR_ERR_SCRATCH_LIMIT (-11)
 #define MVR_ERR_SCRATCH_ADDRESS (-12)
+#define MVR_ERR_UNSUPPORTED (-13)     /* the entry point has no kernel for this shape: use the general one */
+
+/* element types of label volumes (mvr_affine_label_*) */
+#define MVR_LABEL_U8 0
+#define MVR_LABEL_I16 1
+#define MVR_LABEL_I32 2
+#define MVR_LABEL_I64 3
 
 #define MVR_STATUS_BAD_BATCH_INDEX 1
 
@@ -191,6 +198,23 @@ int mvr_affine_3d(const void* input, const void* rois, void* output, int dtype,
                   int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
                   int od, int oh, int ow, float spatial_scale, int sampling_ratio, int aligned, int order,
                   int* status, void* stream);
+
+/* ---- label volumes -------------------------------------------------------------------- */
+
+/* What the reference's augmentations do to a segmentation field,
+ *     affine_3d(seg.float(), rois, out_size, spatial_scale, 1, aligned, order = 0).int()
+ * (medvision/aug_cuda_batch/aug_spatial.py:158-194 and the `apply_to_seg` twins of the other
+ * transforms), on the integer tensor itself: labels is (N, C, [D,] H, W) of label_dtype, rois is
+ * FLOAT32 (R, 6 | 10) as the reference builds it, output is int32 (R, C, [od,] oh, ow).  Same
+ * float32 geometry and nearest rule as mvr_affine_*; the value is (int32)(float)label.  Replaces
+ * two cast passes and a float resample; has no single counterpart in the reference's extension.
+ * Returns MVR_ERR_UNSUPPORTED for rois with fewer than 32 output elements (use the cast path). */
+int mvr_affine_label_2d(const void* labels, int label_dtype, const float* rois, int32_t* output,
+                        int64_t N, int64_t C, int64_t H, int64_t W, int64_t R, int roi_width,
+                        int oh, int ow, float spatial_scale, int aligned, int* status, void* stream);
+int mvr_affine_label_3d(const void* labels, int label_dtype, const float* rois, int32_t* output,
+                        int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
+                        int od, int oh, int ow, float spatial_scale, int aligned, int* status, void* stream);
 
 /* ---- elastic warp ---------------------------------------------------------------------- */
 

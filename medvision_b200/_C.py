@@ -173,6 +173,48 @@ def affine_3d(input, rois, output, aligned_depth, aligned_height, aligned_width,
          (aligned_depth, aligned_height, aligned_width), spatial_scale, sampling_ratio, aligned, order, True)
 
 
+_LABEL_DTYPES = {torch.uint8: 0, torch.int16: 1, torch.int32: 2, torch.int64: 3}
+
+
+def affine_label(input, rois, output, out_sizes, spatial_scale, aligned):
+    """Nearest resampling of an integer label tensor into an int32 ``output``: the result of the
+    reference's ``affine_*(input.float(), rois, ..., order=0).int()`` without the float copies.
+    ``rois`` is float32.  Not a function of the reference's extension.  Returns False when the
+    library has no label kernel for the shape (the caller then takes the cast path)."""
+    ndim = input.dim() - 2
+    if not input.is_cuda:
+        raise RuntimeError("RoIAlignRotated is not implemented on CPU")
+    code = _LABEL_DTYPES.get(input.dtype)
+    if code is None:
+        raise RuntimeError(f'"affine_label" not implemented for \'{str(input.dtype).replace("torch.", "")}\'')
+    width = 6 if ndim == 2 else 10
+    if rois.dim() != 2 or rois.size(1) != width:
+        raise RuntimeError(f"wrong roi size! size_rois should be {width}")
+    if rois.dtype != torch.float32 or output.dtype != torch.int32:
+        raise RuntimeError("affine_label: rois must be float32 and the output int32")
+    if rois.device != input.device or output.device != input.device:
+        raise RuntimeError("expected all tensors to be on the same CUDA device")
+    if not input.is_contiguous():
+        input = input.contiguous()
+    if not rois.is_contiguous():
+        rois = rois.contiguous()
+    R = rois.shape[0]
+    if not output.is_contiguous() or output.shape != (R, input.shape[1], *out_sizes):
+        raise RuntimeError("affine_label: the output must be a contiguous (R, C, *out_size) tensor")
+    device = input.device
+    index = device.index
+    args = (input.data_ptr(), code, rois.data_ptr(), output.data_ptr(), *input.shape, R, width, *out_sizes,
+            float(spatial_scale), 1 if aligned else 0, _status_ptr(device))
+    fn = _FN["mvr_affine_label_%dd" % ndim]
+    with torch.cuda.device(index):
+        rc = fn(*args, _raw_stream(index))
+    if rc == _lib.MVR_ERR_UNSUPPORTED:
+        return False
+    if rc != 0:
+        raise RuntimeError(_lib.strerror(rc))
+    return True
+
+
 def apply_offset(input, offset, order):
     """Displacement-field warp: ``out[b, c, p] = interp(input[b, c], p + offset[b, :, p])``.  Not a
     function of the reference's extension: it is what ``deform_2d`` / ``deform_3d`` compute in the

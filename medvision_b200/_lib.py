@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(HERE, "libmvr.so")
 MVR_F32, MVR_F16, MVR_F64 = 0, 1, 2
 MVR_ROI_BOX, MVR_ROI_ROTATED = 0, 1
 MVR_ERR_ROI_WIDTH = -7
+MVR_ERR_UNSUPPORTED = -13
 MVR_STATUS_BAD_BATCH_INDEX = 1
 
 _i64, _i32, _f32, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
@@ -41,6 +42,9 @@ PROTOTYPES = {
     "mvr_roi_align_rotated_3d_backward": _ROT3D,
     "mvr_apply_offset_2d": [_vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _vp],
     "mvr_apply_offset_3d": [_vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
+    "mvr_affine_label_2d": [_vp, _i32, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _vp],
+    "mvr_affine_label_3d": [_vp, _i32, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _f32,
+                            _i32, _vp, _vp],
     "mvr_affine_2d": _ROT2D,
     "mvr_affine_3d": _ROT3D,
 }

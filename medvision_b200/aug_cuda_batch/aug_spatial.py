@@ -17,7 +17,8 @@ import numpy as np
 import torch
 
 from .base import BatchCudaAugBase
-from ..ops.cuda_fun_tools import affine_2d, affine_3d, apply_offset_2d, apply_offset_3d
+from ..ops.cuda_fun_tools import (affine_2d, affine_3d, affine_label_2d, affine_label_3d, apply_offset_2d,
+                                  apply_offset_3d)
 
 
 def _resample_fields(result, dim, rois, out_size, sampling_ratio, order):
@@ -32,8 +33,9 @@ def _resample_fields(result, dim, rois, out_size, sampling_ratio, order):
         image = result[key]
         assert image.is_cuda, 'image should be cuda'
         assert image.ndim == dim + 2, 'image should be batch, channel, **dim'
-        seg = fn(image.float(), rois.to(image.device, non_blocking=True), out_size, 1.0, sampling_ratio, True, 0)
-        result[key] = seg.int()
+        # = fn(image.float(), rois, out_size, 1.0, 1, True, 0).int() of the reference, on the integers themselves
+        label_fn = affine_label_2d if dim == 2 else affine_label_3d
+        result[key] = label_fn(image, rois.to(image.device, non_blocking=True), out_size, 1.0, True)
     for key in result.get('det_fields', []):
         raise NotImplementedError
 

@@ -12,6 +12,7 @@
 #include "mvr_offset.cuh"
 #include "mvr_cubic3d.cuh"
 #include "mvr_flat.cuh"
+#include "mvr_label.cuh"
 
 // ---- scratch of the entry point that allocates nothing ------------------------------------
 // Lives in the library image: every GPU that loads the library holds these 16 MiB until the
@@ -163,6 +164,7 @@ const char* mvr_strerror(int code) {
       return "gradient volume larger than the built-in scratch of mvr_roi_resample_bwd_noalloc "
              "(4194304 elements): use mvr_roi_resample_bwd, or split the batch";
     case MVR_ERR_SCRATCH_ADDRESS: return "the device address of the built-in scratch could not be obtained";
+    case MVR_ERR_UNSUPPORTED: return "this entry point has no kernel for the given shape";
     default: return "unknown error";
   }
 }
@@ -248,6 +250,31 @@ int mvr_roi_resample_bwd_noalloc(const void* grad_out, const void* rois, void* g
     case MVR_F16: return launch_generic<__half>(p, false, st);
     default: return launch_generic<double>(p, false, st);
   }
+}
+
+static int affine_label_impl(const void* labels, int label_dtype, const float* rois, int32_t* output, int ndim,
+                             int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od,
+                             int oh, int ow, float spatial_scale, int aligned, int* status, void* stream) {
+  if (label_dtype < MVR_LABEL_U8 || label_dtype > MVR_LABEL_I64) return MVR_ERR_DTYPE;
+  int rc = check_common(labels, rois, output, MVR_F32, ndim, MVR_ROI_ROTATED, N, C, D, H, W, R, roi_width, od, oh, ow, 0);
+  if (rc != MVR_OK) return rc;
+  Params p = make_params(labels, rois, output, ndim, MVR_ROI_ROTATED, N, C, D, H, W, R, od, oh, ow, spatial_scale, 1,
+                         aligned, 0, status);
+  rc = launch_label(p, label_dtype, (cudaStream_t)stream);
+  return rc == 0 ? MVR_OK : (rc == -9 ? MVR_ERR_UNSUPPORTED : MVR_ERR_LAUNCH);
+}
+
+int mvr_affine_label_2d(const void* labels, int label_dtype, const float* rois, int32_t* output, int64_t N, int64_t C,
+                        int64_t H, int64_t W, int64_t R, int roi_width, int oh, int ow, float spatial_scale,
+                        int aligned, int* status, void* stream) {
+  return affine_label_impl(labels, label_dtype, rois, output, 2, N, C, 1, H, W, R, roi_width, 1, oh, ow,
+                           spatial_scale, aligned, status, stream);
+}
+int mvr_affine_label_3d(const void* labels, int label_dtype, const float* rois, int32_t* output, int64_t N, int64_t C,
+                        int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od, int oh, int ow,
+                        float spatial_scale, int aligned, int* status, void* stream) {
+  return affine_label_impl(labels, label_dtype, rois, output, 3, N, C, D, H, W, R, roi_width, od, oh, ow,
+                           spatial_scale, aligned, status, stream);
 }
 
 static int apply_offset_impl(const void* img, const void* offset, void* out, int dtype, int offset_dtype, int ndim,

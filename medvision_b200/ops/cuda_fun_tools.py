@@ -61,3 +61,26 @@ def apply_offset_3d(img, offset, order=1):
     """3D: ``img`` (B, C, D, H, W), ``offset`` (B, 3, D, H, W) = (dd, dh, dw).  Same signature as
     medvision/ops/cuda_fun_tools.py:133."""
     return _apply_offset(3, img, offset, order)
+
+
+def _affine_label(ndim, seg, rois, out_size, spatial_scale, aligned):
+    assert seg.dim() == ndim + 2 and len(out_size) == ndim
+    rois = rois.to(device=seg.device, dtype=torch.float32)
+    if seg.dtype in _C._LABEL_DTYPES:
+        out = torch.empty((rois.shape[0], seg.shape[1], *out_size), dtype=torch.int32, device=seg.device)
+        if _C.affine_label(seg, rois, out, tuple(int(v) for v in out_size), spatial_scale, aligned):
+            return out
+    fn = affine_2d if ndim == 2 else affine_3d
+    return fn(seg.float(), rois, out_size, spatial_scale, 1, aligned, 0).int()
+
+
+def affine_label_2d(seg, rois, out_size, spatial_scale=1.0, aligned=True):
+    """Label map (N, C, H, W) of an integer dtype -> int32 (R, C, oh, ow): what the reference's
+    augmentations compute as ``affine_2d(seg.float(), rois, out_size, spatial_scale, 1, aligned,
+    0).int()`` (medvision/aug_cuda_batch/aug_spatial.py:158-194), in one kernel on the integers."""
+    return _affine_label(2, seg, rois, out_size, spatial_scale, aligned)
+
+
+def affine_label_3d(seg, rois, out_size, spatial_scale=1.0, aligned=True):
+    """3D: (N, C, D, H, W) -> int32 (R, C, od, oh, ow)."""
+    return _affine_label(3, seg, rois, out_size, spatial_scale, aligned)

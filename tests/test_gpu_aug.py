@@ -150,3 +150,51 @@ def test_elastic_deformation(shape, dtype):
     assert torch.equal(t.tmp_params, -dense) and t.key_name not in back
     assert n_mismatch(back["img"], port.apply_offset(warped, -dense, 1, fma_mode=fm)) == 0
     assert torch.equal(back["gt_seg"].cpu(), port.apply_offset(warped_seg.to(dtype), -dense, 0, fma_mode=fm).int())
+
+
+LABEL_CASES = [
+    # spatial, out_size, rotation kind
+    ((12, 40, 48), (16, 32, 40), "planar"),
+    ((12, 40, 48), (16, 32, 40), "general"),
+    ((10, 22, 27), (12, 20, 23), "planar"),      # odd width: scalar stores
+    ((9, 12, 14), (3, 4, 5), "general"),         # small output: flat kernel
+    ((40, 48), (32, 36), "planar"),
+]
+
+
+@pytest.mark.parametrize("spatial,out_size,rot", LABEL_CASES)
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.int16, torch.int32, torch.int64])
+def test_label_resample_equals_float_nearest_path(spatial, out_size, rot, dtype):
+    """affine_label_* on the integer tensor = affine_*(seg.float(), ..., order=0).int(): against the
+    restatement, the library's own float path and, when present, the reference's kernels."""
+    from medvision_b200.ops import affine_2d, affine_3d, affine_label_2d, affine_label_3d
+    from oracle import ref
+    ndim = len(spatial)
+    g = torch.Generator().manual_seed(hash((spatial, out_size, rot)) % 1000)
+    hi = {torch.uint8: 255, torch.int16: 3000, torch.int32: 70000, torch.int64: 1 << 20}[dtype]
+    seg = torch.randint(0, hi, (2, 2) + spatial, generator=g).to(dtype)
+    R = 5
+    b = torch.randint(0, 2, (R, 1), generator=g).float()
+    centre = torch.tensor(spatial[::-1], dtype=torch.float32) * (0.3 + 0.4 * torch.rand(R, ndim, generator=g))
+    size = torch.tensor(spatial[::-1], dtype=torch.float32) * (0.5 + torch.rand(R, ndim, generator=g))
+    if ndim == 2:
+        ang = (torch.rand(R, 1, generator=g) - 0.5) * 1.5
+    else:
+        ang = (torch.rand(R, 3, generator=g) - 0.5) * 1.2
+        if rot == "planar":
+            ang[:, :2] = 0
+    rois = torch.cat([b, centre, size, ang], 1)
+    rois[R - 1, 0] = 7  # a batch index outside the batch: zeros
+    fn, lab = (affine_2d, affine_label_2d) if ndim == 2 else (affine_3d, affine_label_3d)
+    got = lab(seg.cuda(), rois.cuda(), out_size)
+    assert got.dtype == torch.int32 and got.shape == (R, 2) + out_size
+    good = rois[:R - 1]
+    want = port.forward(seg.float(), good, out_size, port.KIND_ROTATED, 1.0, 1, True, 0, trig=port.device_trig(good),
+                        fma_mode=REF_FM).int()
+    assert torch.equal(got[:R - 1].cpu(), want)
+    assert torch.equal(got, fn(seg.cuda().float(), rois.cuda(), out_size, 1.0, 1, True, 0).int())
+    assert not bool(got[R - 1].any())
+    if ref.available():
+        live = ref.forward(seg.cuda().float(), rois[:R - 1].cuda(), out_size, port.KIND_ROTATED, 1.0, 1, True, 0,
+                           affine=True).int()
+        assert torch.equal(got[:R - 1], live)
