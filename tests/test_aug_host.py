@@ -150,3 +150,82 @@ def test_elastic_coarse_field_draws_and_locked_borders(shape, points):
     t._backward_params(res)
     assert t.tmp_params is None and t.key_name not in res
     assert t.canBackward
+
+
+# ----------------------------------------------------------------------------- single-sample classes
+def _sample(shape=(1, 8, 10, 12)):
+    return {"img_dim": len(shape) - 1, "img": torch.zeros(shape), "img_fields": ["img"], "seg_fields": [],
+            "img_spacing": (1.0,) * (len(shape) - 1)}
+
+
+def test_single_sample_transforms_draw_like_their_batched_twins():
+    """One sample = a batch of one: same draws from numpy's generator, same roi."""
+    from medvision_b200.aug_cuda import (CudaCropCenterWithAffine, CudaCropRandomWithAffine, CudaRandomAffine,
+                                         CudaResize)
+    np.random.seed(4)
+    single = CudaRandomAffine(1.0, scale=0.2, shift=0.1, rotate=30)
+    single._forward_params(_sample())
+    np.random.seed(4)
+    batched = BatchCudaRandomAffine(1.0, scale=0.2, shift=0.1, rotate=30)
+    batched._forward_params(_result((1, 1, 8, 10, 12)))
+    assert torch.equal(single._rois(), batched._rois())
+    assert set(single.params) == {"_scales", "_shifts", "_rotate"} and len(single.params["_shifts"]) == 3
+
+    np.random.seed(5)
+    crop = CudaCropRandomWithAffine(patch_size=(4, 6, 6), scale=0.1, shift=0.05, rotate=15)
+    crop._forward_params(_sample())
+    np.random.seed(5)
+    bcrop = BatchCudaCropRandomWithAffine(patch_size=(4, 6, 6), scale=0.1, shift=0.05, rotate=15)
+    bcrop._forward_params(_result((1, 1, 8, 10, 12)))
+    assert torch.allclose(crop._rois(), bcrop._rois())
+    start, end = crop.params["start"], crop.params["end"]  # xyz
+    assert all(e - s == p for s, e, p in zip(start, end, (6, 6, 4)))
+
+    centre = CudaCropCenterWithAffine(patch_size=(4, 6, 6), scale=0, shift=0, rotate=0)
+    centre._forward_params(_sample())
+    assert centre.params["start"] == (3, 2, 2) and centre.params["end"] == (9, 8, 6)
+    assert torch.equal(centre._rois(), torch.tensor([[0, 6., 5., 4., 6., 6., 4., 0., 0., 0.]]))
+
+    resize = CudaResize(factor=(0.5, 0.5, 0.25))
+    resize._forward_params(_sample())
+    assert torch.equal(resize._rois(), torch.tensor([[0, 6., 5., 4., 12., 10., 8., 0., 0., 0.]]))
+
+
+def test_crop_around_the_first_detection_box():
+    from medvision_b200.aug_cuda import CudaCropFirstDetWithAffine
+    t = CudaCropFirstDetWithAffine(border=1, patch_size=(4, 6, 6), scale=0, shift=0, rotate=0)
+    res = _sample()
+    res["gt_det"] = torch.tensor([[7., 5., 3., 9., 7., 5., 1., 1.]])  # x1 y1 z1 x2 y2 z2 label score
+    for seed in range(20):
+        np.random.seed(seed)
+        t._forward_params(res)
+        (sx, sy, sz), (ex, ey, ez) = t.params["start"], t.params["end"]
+        assert (ex - sx, ey - sy, ez - sz) == (6, 6, 4)
+        # the box plus its border stays inside the patch wherever the image leaves room
+        assert sx <= 6 and ex >= 10 and sy <= 4 and ey >= 8 and sz <= 2 + 1 and ez >= 6 - 1
+        assert 0 <= sx and ex <= 12 and 0 <= sy and ey <= 10 and 0 <= sz and ez <= 8
+    res["gt_det"] = torch.zeros(0, 8)
+    t._forward_params(res)  # no box: a random crop
+
+
+def test_repeats_make_a_list_of_results_without_copying_tensors():
+    from medvision_b200.aug_cuda import CudaAugBase
+
+    class Tag(CudaAugBase):
+        def __init__(self):
+            super().__init__()
+            self.always = True
+
+        @property
+        def repeats(self):
+            return 3
+
+        def _forward_params(self, result):
+            result[self.key_name] = np.random.rand()
+
+    res = _sample()
+    out = Tag()(res)
+    assert isinstance(out, list) and len(out) == 3
+    assert all(o["img"] is res["img"] for o in out)
+    assert len({o["Tag_params"] for o in out}) == 3
+    assert all(o["history"] == ["Tag"] for o in out) and "history" not in res

@@ -198,3 +198,56 @@ def test_label_resample_equals_float_nearest_path(spatial, out_size, rot, dtype)
         live = ref.forward(seg.cuda().float(), rois[:R - 1].cuda(), out_size, port.KIND_ROTATED, 1.0, 1, True, 0,
                            affine=True).int()
         assert torch.equal(got[:R - 1], live)
+
+
+def _single(shape, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    return {"img_dim": len(shape) - 1, "img": torch.rand(shape, generator=g).to(dtype).cuda(), "img_fields": ["img"],
+            "gt_seg": torch.randint(0, 5, shape, generator=g, dtype=torch.int32).cuda(), "seg_fields": ["gt_seg"],
+            "img_spacing": (1.0,) * (len(shape) - 1)}
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_single_sample_transforms_equal_the_batched_ones_on_a_batch_of_one(dtype):
+    import medvision_b200.aug_cuda as one
+    import medvision_b200.aug_cuda_batch as many
+    shape = (2, 12, 24, 32)
+    pairs = [
+        (one.CudaResize(factor=(0.5, 0.75, 0.5)), many.BatchCudaResize(factor=(0.5, 0.75, 0.5))),
+        (one.CudaRandomAffine(1.0, 0.2, 0.1, 25), many.BatchCudaRandomAffine(1.0, 0.2, 0.1, 25)),
+        (one.CudaRandomRotate(1.0, 40), many.BatchCudaRandomRotate(1.0, 40)),
+        (one.CudaCropRandomWithAffine((8, 16, 16), 0.1, 0.05, 20),
+         many.BatchCudaCropRandomWithAffine((8, 16, 16), 0.1, 0.05, 20)),
+        (one.CudaCropCenterWithAffine((8, 16, 16), 0.1, 0.05, 20),
+         many.BatchCudaCropCenterWithAffine((8, 16, 16), 0.1, 0.05, 20)),
+        (one.CudaRandomElasticDeformation(1.0, 7, 0.9), many.BatchCudaRandomElasticDeformation(1.0, 7, 0.9)),
+    ]
+    for k, (a, b) in enumerate(pairs):
+        ra = _single(shape, dtype, 30 + k)
+        rb = {"img_dim": 3, "img": ra["img"].unsqueeze(0), "img_fields": ["img"],
+              "gt_seg": ra["gt_seg"].unsqueeze(0), "seg_fields": ["gt_seg"], "img_spacing": (1.0, 1.0, 1.0)}
+        np.random.seed(100 + k)
+        ra = a(ra)
+        np.random.seed(100 + k)
+        rb = b(rb)
+        assert torch.equal(ra["img"], rb["img"][0]), a.name
+        assert ra["gt_seg"].dtype == torch.int32 and torch.equal(ra["gt_seg"], rb["gt_seg"][0]), a.name
+        assert ra["history"] == [a.name]
+        if "Elastic" not in a.name:
+            assert ra["img_shape"] == tuple(ra["img"].shape)
+
+
+def test_single_sample_crop_repeats_and_resize_backward():
+    import medvision_b200.aug_cuda as one
+    res = _single((1, 16, 32, 32), torch.float16, 41)
+    np.random.seed(7)
+    crops = one.CudaCropRandomWithAffine((8, 16, 16), 0.1, 0.05, 20, times=3)(res)
+    assert len(crops) == 3 and all(c["img"].shape == (1, 8, 16, 16) and c["gt_seg"].shape == (1, 8, 16, 16) for c in crops)
+    assert not torch.equal(crops[0]["img"], crops[1]["img"])
+    assert res["img"].shape == (1, 16, 32, 32)  # the source sample is left as it was
+    t = one.CudaResize(factor=(0.5, 0.5, 0.5))
+    small = t(_single((1, 16, 32, 32), torch.float32, 42))
+    assert small["img"].shape == (1, 8, 16, 16) and small["img_spacing"] == (2.0, 2.0, 2.0)
+    back = t(small, forward=False)
+    assert back["img"].shape == (1, 16, 32, 32) and back["gt_seg"].shape == (1, 16, 32, 32)
+    assert back["history"] == [] and t.key_name not in back
