@@ -335,3 +335,39 @@ def test_full_size_resize_slab_against_restatement():
     assert n_mismatch(small, oracle) == 0
     # interior of the big result equals the small one where both read the same voxels
     assert n_mismatch(out[0, 0, :, :31, :31], small[0, 0, :, :31, :31]) == 0
+
+
+def test_volume_beyond_two_to_the_31_elements():
+    """One channel of 2050 x 1024 x 1024 floats (2.15e9 elements, 8.6 GB): flat offsets no longer fit
+    32 bits (the reference's int index overflows here, medvision/csrc/cuda/cuda_helpers.h:10-12).
+    A roi at the far end of the volume must give what the same roi gives on the last 24 planes
+    alone (coordinates shifted by the crop, so equal up to float rounding of the z coordinate)."""
+    D, H, W, keep = 2050, 1024, 1024, 24
+    if torch.cuda.mem_get_info()[0] < 24 * 2 ** 30:
+        pytest.skip("needs 24 GB of free device memory")
+    big = torch.zeros((1, 1, D, H, W), dtype=torch.float32, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    tail = torch.rand((1, 1, keep, H, W), generator=g, device="cuda")
+    big[:, :, D - keep:] = tail
+    for angles, order in (((0.0, 0.0, 0.3), 1), ((0.2, -0.1, 0.3), 1), ((0.0, 0.0, 0.3), 0)):
+        roi = torch.tensor([[0, 900.0, 800.0, D - 10.0, 64.0, 48.0, 12.0, *angles]], device="cuda")
+        small_roi = roi.clone()
+        small_roi[0, 3] -= D - keep
+        for out_size in ((6, 24, 32), (3, 5, 7)):  # dense shape (falls back to 64-bit offsets) and head-sized
+            a = lib_forward(big, roi, out_size, cases.KIND_ROTATED, order=order, sampling_ratio=1)
+            b = lib_forward(tail, small_roi, out_size, cases.KIND_ROTATED, order=order, sampling_ratio=1)
+            assert float(a.abs().max()) > 0.1
+            if order == 1:
+                torch.testing.assert_close(a, b, rtol=0, atol=2e-3)
+            else:
+                assert float((a != b).float().mean()) < 0.02  # a rounding of z flips a nearest pick now and then
+        # gradient: everything lands in the last planes, nothing before them
+        grad = torch.ones((1, 1, 3, 5, 7), device="cuda")
+        gin = lib_backward(grad, roi, big.shape, cases.KIND_ROTATED, order=order, sampling_ratio=1)
+        assert float(gin[:, :, :D - keep].abs().max()) == 0.0
+        gs = lib_backward(grad, small_roi, tail.shape, cases.KIND_ROTATED, order=order, sampling_ratio=1)
+        if order == 1:
+            torch.testing.assert_close(gin[:, :, D - keep:], gs, rtol=0, atol=2e-3)
+        del gin, gs
+    del big, tail
+    torch.cuda.empty_cache()
