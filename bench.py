@@ -134,6 +134,9 @@ class Ours:
         from medvision_b200.ops import affine_label_3d
         return affine_label_3d(seg, rois, tuple(out_size))
 
+    def forward2d_into(self, feat, rois, out, order):
+        self._C.affine_2d(feat, rois, out, *out.shape[2:], 1.0, 1, True, order)
+
     def host_forward(self, feat_h, rois_h, out_size, order, out_h):
         """host tensors in, host tensor out: the library's pipelined entry point"""
         from medvision_b200.ops import affine_from_host
@@ -166,6 +169,9 @@ class ReferenceCuda:
     def label_forward(self, seg, rois, out_size):
         """apply_to_seg of the reference's transforms (medvision/aug_cuda_batch/aug_spatial.py:158-194)"""
         return self.public_forward(seg.float(), rois, out_size, 0).int()
+
+    def forward2d_into(self, feat, rois, out, order):
+        self.m.affine_2d(feat, rois, out, *out.shape[2:], 1.0, 1, True, order)
 
 
 # ----------------------------------------------------------------------------- measurement
@@ -452,6 +458,25 @@ def label_config(impl, peak):
              "note": "public call; the reference arm runs seg.float() -> affine_3d(order 0) -> .int()"}]
 
 
+def dense2d_config(impl, peak):
+    """2D RandomAffine on 16 half images (1,2048,2048): rotation +-20 degrees, scale 0.9-1.1, shift +-10 px."""
+    B, H, W = 16, 2048, 2048
+    img = ct_like((B, 1, 1, H, W), 21, "cuda").reshape(B, 1, H, W)
+    g = torch.Generator().manual_seed(22)
+    scale = 0.9 + 0.2 * torch.rand(B, 1, generator=g)
+    rois = torch.cat([torch.arange(B).float()[:, None],
+                      torch.tensor([[W / 2, H / 2]]).repeat(B, 1) + (torch.rand(B, 2, generator=g) - 0.5) * 20,
+                      torch.tensor([[float(W), float(H)]]).repeat(B, 1) / scale,
+                      (torch.rand(B, 1, generator=g) - 0.5) * 0.7], 1).half().cuda()
+    out = torch.empty_like(img)
+    ms = time_steps(lambda: impl.forward2d_into(img, rois, out, 1), 50, 5, 1) / 50
+    n = out.numel()
+    alg = 2 * 2 * n  # every pixel read about once, every output written once
+    return [{"workload": "2D RandomAffine: 16x(1,2048,2048) fp16 -> same, linear", "pass": "fwd", "ms_per_step": ms,
+             "gvoxel_per_s": n / (ms * 1e-3) / 1e9, "algorithmic_bytes": alg, "achieved_gbs": alg / (ms * 1e-3) / 1e9,
+             "frac_of_peak": alg / (ms * 1e-3) / 1e9 / peak, "note": "input larger than L2; issue-bound"}]
+
+
 def cpu_baseline_scipy():
     """What the reference's numpy augmentations call for the same job
     (medvision/aug_cpu/aug_spatial.py:475 rotate, :99 zoom), single-threaded scipy."""
@@ -556,7 +581,8 @@ def main():
     if args.workload == "elastic":
         if rank == 0:
             print(json.dumps({"impl": args.impl, "elastic": elastic_config(impl, load_peaks()[0]),
-                              "label": label_config(impl, load_peaks()[0])}))
+                              "label": label_config(impl, load_peaks()[0]),
+                              "dense2d": dense2d_config(impl, load_peaks()[0])}))
         return
     sampler = ClockSampler(local)
     if rank == 0:
@@ -629,6 +655,7 @@ def main():
                               "note": "input fits in L2" if key == "c4" else "input larger than L2"})
             extra += elastic_config(impl, peak)
             extra += label_config(impl, peak)
+            extra += dense2d_config(impl, peak)
             det = detection_configs(args.impl)
             if det:
                 extra += det

@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmvr.so")
 SOURCES = ["mvr_api.cu"]
-HEADERS = ["mvr_arith.cuh", "mvr_geom.cuh", "mvr_generic.cuh", "mvr_stream3d.cuh", "mvr_tma3d.cuh", "mvr_bwd3d.cuh", "mvr_offset.cuh", "mvr_cubic3d.cuh", "mvr_flat.cuh", "mvr_label.cuh",
+HEADERS = ["mvr_arith.cuh", "mvr_geom.cuh", "mvr_generic.cuh", "mvr_stream3d.cuh", "mvr_tma3d.cuh", "mvr_bwd3d.cuh", "mvr_offset.cuh", "mvr_cubic3d.cuh", "mvr_flat.cuh", "mvr_label.cuh", "mvr_plane2d.cuh",
            os.path.join("..", "..", "include", "mvr.h")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

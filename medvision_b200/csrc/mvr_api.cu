@@ -13,6 +13,7 @@
 #include "mvr_cubic3d.cuh"
 #include "mvr_flat.cuh"
 #include "mvr_label.cuh"
+#include "mvr_plane2d.cuh"
 
 // ---- scratch of the entry point that allocates nothing ------------------------------------
 // Lives in the library image: every GPU that loads the library holds these 16 MiB until the
@@ -117,6 +118,8 @@ int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
     const int rc = fwd ? try_launch_stream3d(p, dtype, st) : try_launch_bwd_stream3d(p, dtype, st);
     if (rc != MVR_STREAM3D_NOT_APPLICABLE) return rc;
   }
+  if (fwd && try_launch_plane2d(p, dtype, st) == 0)
+    return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
   if (fwd && p.order == 3 && p.ndim == 3) {
     int rc;
     switch (dtype) {

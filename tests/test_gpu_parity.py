@@ -371,3 +371,60 @@ def test_volume_beyond_two_to_the_31_elements():
         del gin, gs
     del big, tail
     torch.cuda.empty_cache()
+
+
+def dense_case_2d(kind, dtype, out_size, spatial, seed, R=5, C=3, N=2, scale=1.0, rotate=True):
+    g = torch.Generator().manual_seed(seed)
+    H, W = spatial
+    feat = (torch.rand((N, C, H, W), generator=g, dtype=torch.float64) * 2 - 0.5).to(dtype)
+    ext = torch.tensor([W, H], dtype=torch.float64)
+    b = torch.randint(0, N, (R, 1), generator=g).double()
+    centre = ext / 2 + (torch.rand(R, 2, generator=g, dtype=torch.float64) - 0.5) * ext * 0.6
+    size = ext * (0.4 + 0.9 * torch.rand(R, 2, generator=g, dtype=torch.float64))
+    if kind == cases.KIND_BOX:
+        rois = torch.cat([b, (centre - size / 2) / scale, (centre + size / 2) / scale], 1)
+    else:
+        ang = (torch.rand(R, 1, generator=g, dtype=torch.float64) * 2 - 1) * math.pi * 0.9
+        if not rotate:
+            ang[:] = 0
+        ang[0] = 0
+        rois = torch.cat([b, centre / scale, size / scale, ang], 1)
+    return feat, rois.to(dtype)
+
+
+PLANE = []
+for dtype in (torch.float16, torch.float32):
+    for kind in (cases.KIND_ROTATED, cases.KIND_BOX):
+        for order in (1, 0):
+            PLANE.append((dtype, kind, order, (72, 80), (60, 90), 1.0, 3))
+    PLANE.append((dtype, cases.KIND_ROTATED, 1, (150, 67), (130, 75), 0.77, 1))   # odd width, several row blocks
+    PLANE.append((dtype, cases.KIND_ROTATED, 1, (64, 64), (300, 500), 1.0, 2))    # strong down-sampling
+    PLANE.append((dtype, cases.KIND_BOX, 1, (260, 40), (33, 35), 1.0, 1))         # up-sampling, tall
+
+
+@pytest.mark.parametrize("dtype,kind,order,out_size,spatial,scale,channels", PLANE,
+                         ids=["%s-%s-o%d-%s" % (str(s[0])[6:], "rot" if s[1] else "box", s[2],
+                                                "x".join(map(str, s[3]))) for s in PLANE])
+def test_dense_2d_kernel_matches_restatement_and_reference(dtype, kind, order, out_size, spatial, scale, channels):
+    feat, rois = dense_case_2d(kind, dtype, out_size, spatial, seed=51 + order + spatial[1], C=channels, scale=scale)
+    kw = dict(spatial_scale=scale, sampling_ratio=1, aligned=True, order=order)
+    bad = rois.clone()
+    bad[-1, 0] = 9  # batch index outside the batch: zeros
+    out = lib_forward(feat.cuda(), bad.cuda(), out_size, kind, **kw)
+    assert not torch.isnan(out).any(), "every output element must be written"
+    assert not bool(out[-1].any())
+    good = rois[:-1]
+    trig = port.device_trig(good) if kind == cases.KIND_ROTATED else None
+    oracle = port.forward(feat, good, out_size, kind, trig=trig, fma_mode=REF_FM if dtype == torch.float32 else 0, **kw)
+    assert n_mismatch(out[:-1], oracle) == 0, "bit-exact against the CPU restatement"
+    if ref.available():
+        r = ref.forward(feat.cuda(), good.cuda(), out_size, kind, **kw)
+        assert n_mismatch(out[:-1], r) == 0, "bit-exact against the reference's own kernel"
+    # a view whose storage starts one element into an allocation: scalar stores
+    buf = torch.empty(out.numel() + 1, dtype=dtype, device="cuda")
+    from medvision_b200 import _C
+    o2 = buf[1:].view(out.shape)
+    fn = _C.roi_align_rotated_2d_forward if kind == cases.KIND_ROTATED else _C.roi_align_2d_forward
+    args = (feat.cuda(), bad.cuda(), o2, *out_size, scale, 1) + ((True,) if kind == cases.KIND_ROTATED else ()) + (order,)
+    fn(*args)
+    assert torch.equal(o2, out)
