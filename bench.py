@@ -560,8 +560,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["elastic"], default="c5",
-                    help="elastic: only the elastic deformation's two steps, one GPU (profiling aid)")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["elastic", "det"], default="c5",
+                    help="elastic / det: only the elastic, label and 2D entries / only the detection-head "
+                         "configurations of other_configs, one GPU (profiling aids)")
     ap.add_argument("--small", action="store_true", help="reduced copy of the workload (for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true", help="skip e2e, CPU baselines and the extra configurations")
     ap.add_argument("--backward", action="store_true", help="time forward + backward instead of forward (profiling aid)")
@@ -578,6 +579,10 @@ def main():
 
     rank, world, local = dist_setup(args.gpus)
     impl = Ours() if args.impl == "ours" else ReferenceCuda()
+    if args.workload == "det":
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "detection": detection_configs(args.impl)}))
+        return
     if args.workload == "elastic":
         if rank == 0:
             print(json.dumps({"impl": args.impl, "elastic": elastic_config(impl, load_peaks()[0]),
@@ -603,7 +608,7 @@ def main():
                        "l2": "inputs (%.2f GB per GPU) larger than L2, no flush" %
                              (wl["features"].numel() * 2 / 1e9),
                        "sampling_ratio": 1, "order": 1, "aligned": True},
-            "gpu_launches": 2 * args.steps, "clocks": clocks}
+            "gpu_launches": (2 if args.impl == "ours" else 1) * args.steps, "clocks": clocks}
     if args.impl == "reference":
         line["impl"] = "reference"
         line["config"]["device"] = "cuda: the reference's own kernels, compiled unmodified for sm_100a"

@@ -80,7 +80,9 @@ resample_flat(const Params p, int per_roi) {
     if (BWD) {
       if (!in) return;
 #pragma unroll
-      for (int k = 0; k < (1 << NDIM); ++k) atomic_add_T(gvol + off[k], A::div(A::mul(go, w[k]), g.count_bwd));
+      for (int k = 0; k < (1 << NDIM); k += 2)
+        atomic_add_pair(gvol + off[k], gvol + off[k + 1], A::div(A::mul(go, w[k]), g.count_bwd),
+                        A::div(A::mul(go, w[k + 1]), g.count_bwd));
     } else {
       T val = zero;
       if (in) {

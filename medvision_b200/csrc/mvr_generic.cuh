@@ -137,6 +137,31 @@ __device__ __forceinline__ void atomic_add_T(float* p, float v) { atomicAdd(p, v
 __device__ __forceinline__ void atomic_add_T(double* p, double v) { atomicAdd(p, v); }
 __device__ __forceinline__ void atomic_add_T(__half* p, __half v) { atomicAdd(p, v); }
 
+// The two x-neighbours of a tap row.  When they are adjacent in memory and the lower one is
+// aligned to the pair, both go out as ONE element-type reduction on one L2 sector (float: two
+// 32-bit lanes, half: a packed pair) instead of two; each lane is still an element-type add in
+// whatever order the hardware serves it, as with the reference's scalar atomics.
+__device__ __forceinline__ void atomic_add_pair(float* p0, float* p1, float v0, float v1) {
+  if (p1 == p0 + 1 && (reinterpret_cast<unsigned long long>(p0) & 7ull) == 0) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p0), "f"(v0), "f"(v1) : "memory");
+  } else {
+    atomicAdd(p0, v0);
+    atomicAdd(p1, v1);
+  }
+}
+__device__ __forceinline__ void atomic_add_pair(__half* p0, __half* p1, __half v0, __half v1) {
+  if (p1 == p0 + 1 && (reinterpret_cast<unsigned long long>(p0) & 3ull) == 0) {
+    atomicAdd(reinterpret_cast<__half2*>(p0), __halves2half2(v0, v1));
+  } else {
+    atomicAdd(p0, v0);
+    atomicAdd(p1, v1);
+  }
+}
+__device__ __forceinline__ void atomic_add_pair(double* p0, double* p1, double v0, double v1) {
+  atomicAdd(p0, v0);
+  atomicAdd(p1, v1);
+}
+
 template <typename T, int NDIM>
 __global__ void __launch_bounds__(kGenericThreads)
 resample_bwd_generic(const Params p) {
