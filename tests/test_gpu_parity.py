@@ -428,3 +428,33 @@ def test_dense_2d_kernel_matches_restatement_and_reference(dtype, kind, order, o
     args = (feat.cuda(), bad.cuda(), o2, *out_size, scale, 1) + ((True,) if kind == cases.KIND_ROTATED else ()) + (order,)
     fn(*args)
     assert torch.equal(o2, out)
+
+
+@pytest.mark.parametrize("rot", ["z", "xyz"])
+def test_dense_forward_replays_from_a_cuda_graph(rot):
+    """The dense forward is two launches with a programmatic dependency and no allocation: it can
+    be captured into a CUDA graph and replayed on new data in the same buffers."""
+    from medvision_b200 import _C
+    out_size, spatial = (24, 40, 48), (40, 48, 64)
+    feat, rois = dense_case(cases.KIND_ROTATED, torch.float16, rot, 1, out_size, spatial, seed=5)
+    f, r = feat.cuda(), rois.cuda()
+    out = torch.empty((r.size(0), f.size(1)) + out_size, dtype=f.dtype, device="cuda")
+    _C.affine_3d(f, r, out, *out_size, 1.0, 1, True, 1)  # lazy set-up outside the capture
+    want_first = out.clone()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            _C.affine_3d(f, r, out, *out_size, 1.0, 1, True, 1)
+    torch.cuda.synchronize()
+    out.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want_first)
+    f.mul_(0.5)  # new data, same buffers
+    graph.replay()
+    torch.cuda.synchronize()
+    direct = torch.empty_like(out)
+    _C.affine_3d(f, r, direct, *out_size, 1.0, 1, True, 1)
+    assert torch.equal(out, direct)
