@@ -326,7 +326,7 @@ def cpu_baseline_port(wl, budget_s=15.0):
 
 def cpu_baseline_torch_function():
     """The reference's torch-function RoIAlign path on CPU (restated in oracle/torch_function_path.py)
-    on BASELINE config 1: features (2,4,64,64,64) fp32, 128 rois, output 7^3, forward + backward."""
+    on the RoIAlign 3D head configuration: features (2,4,64,64,64) fp32, 128 rois, output 7^3, forward + backward."""
     from oracle.torch_function_path import config1_inputs, roi_align_torch_function
     feat, rois = config1_inputs()
     feat.requires_grad_(True)
@@ -342,7 +342,7 @@ def cpu_baseline_torch_function():
 
 
 def detection_configs(impl_name):
-    """Latency of the small detection-style configurations (BASELINE configs 1 and 2): forward and
+    """Latency of the small detection-style configurations (RoIAlign 3D and RoIAlignRotated 2D heads): forward and
     forward + backward through the op modules, CUDA events over 200 calls each."""
     if impl_name != "ours":
         return None

@@ -36,7 +36,7 @@ def roi_align_torch_function(feat_map, rois, output_size, spatial_scale=1.0, ord
 
 
 def config1_inputs(n_rois=128, seed=1):
-    """BASELINE config 1: features (2,4,64,64,64) uniform[0,1); rois with batch idx in {0,1}, centres
+    """RoIAlign 3D head configuration: features (2,4,64,64,64) uniform[0,1); rois with batch idx in {0,1}, centres
     uniform in the volume, side lengths uniform 8-48; output 7x7x7."""
     g = torch.Generator().manual_seed(seed)
     feat = torch.rand(2, 4, 64, 64, 64, generator=g)
