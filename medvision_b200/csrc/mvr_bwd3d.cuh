@@ -92,6 +92,26 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
     const int ob[4] = {tyb.i0 * p.W + txb.i0, tyb.i0 * p.W + txb.i1, tyb.i1 * p.W + txb.i0, tyb.i1 * p.W + txb.i1};
     const V lx2 = Q::make(txa.l, txb.l), hx2 = Q::make(txa.h, txb.h);
     const V ly2 = Q::make(tya.l, tyb.l), hy2 = Q::make(tya.h, tyb.h);
+    // Along the depth walk consecutive outputs mostly share a source plane (the upper plane of one
+    // depth is the lower plane of the next, or both planes repeat when up-sampling): the
+    // contributions to the two planes in hand are summed in float registers and go to memory
+    // once, when the walk leaves the plane.
+    float acc0[8], acc1[8];  // [0..3] voxel a, [4..7] voxel b; taps x0y0, x1y0, x0y1, x1y1
+#pragma unroll
+    for (int t = 0; t < 8; ++t) acc0[t] = acc1[t] = 0.0f;
+    long long held0 = -1, held1 = -1;  // plane offsets of acc0 / acc1, -1: nothing held
+    auto flush = [&](const float* a, long long plane) {
+      if (plane < 0) return;
+      Acc* pl = acc + plane;
+      if (ina) {
+        bwd_red_row(pl + oa[0], pl + oa[1], a[0], a[1]);
+        bwd_red_row(pl + oa[2], pl + oa[3], a[2], a[3]);
+      }
+      if (inb) {
+        bwd_red_row(pl + ob[0], pl + ob[1], a[4], a[5]);
+        bwd_red_row(pl + ob[2], pl + ob[3], a[6], a[7]);
+      }
+    };
     for (int i = 0; i < k.npd; ++i) {
       const S3ZTap<T> e = sh.zt[i];
       if (!e.inside) continue;
@@ -104,16 +124,33 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
       // g_k = grad * w_k, each product rounded
       const V w[8] = {Q::mul(hzhy, hx2), Q::mul(hzhy, lx2), Q::mul(hzly, hx2), Q::mul(hzly, lx2),
                       Q::mul(lzhy, hx2), Q::mul(lzhy, lx2), Q::mul(lzly, hx2), Q::mul(lzly, lx2)};
-      Acc* p0 = acc + e.o0;
-      Acc* p1 = acc + e.o1;
+      float c0[8], c1[8];
 #pragma unroll
-      for (int t = 0; t < 8; t += 2) {
-        const V g0 = Q::mul(g2, w[t]), g1 = Q::mul(g2, w[t + 1]);
-        Acc* pl = (t < 4) ? p0 : p1;
-        if (ina) bwd_red_row(pl + oa[t & 3], pl + oa[(t & 3) + 1], A::tof(Q::lo(g0)), A::tof(Q::lo(g1)));
-        if (inb) bwd_red_row(pl + ob[t & 3], pl + ob[(t & 3) + 1], A::tof(Q::hi(g0)), A::tof(Q::hi(g1)));
+      for (int t = 0; t < 4; ++t) {
+        const V lo = Q::mul(g2, w[t]), hi = Q::mul(g2, w[4 + t]);
+        c0[t] = A::tof(Q::lo(lo)); c0[4 + t] = A::tof(Q::hi(lo));
+        c1[t] = A::tof(Q::lo(hi)); c1[4 + t] = A::tof(Q::hi(hi));
+      }
+      if (e.o0 == held0 && e.o1 == held1) {  // CTA-uniform
+#pragma unroll
+        for (int t = 0; t < 8; ++t) { acc0[t] += c0[t]; acc1[t] += c1[t]; }
+      } else if (e.o0 == held1) {
+        flush(acc0, held0);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) { acc0[t] = acc1[t] + c0[t]; acc1[t] = c1[t]; }
+        held0 = held1;
+        held1 = e.o1;
+      } else {
+        flush(acc0, held0);
+        flush(acc1, held1);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) { acc0[t] = c0[t]; acc1[t] = c1[t]; }
+        held0 = e.o0;
+        held1 = e.o1;
       }
     }
+    flush(acc0, held0);
+    flush(acc1, held1);
     return;
   }
 

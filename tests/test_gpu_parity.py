@@ -458,3 +458,25 @@ def test_dense_forward_replays_from_a_cuda_graph(rot):
     direct = torch.empty_like(out)
     _C.affine_3d(f, r, direct, *out_size, 1.0, 1, True, 1)
     assert torch.equal(out, direct)
+
+
+def test_more_rois_than_the_gather_launch_can_mark():
+    """Beyond 16384 rois the second launch of a rotated forward cannot hold its roi marks in shared
+    memory and runs with one CTA per work item instead: same results."""
+    R, out_size, spatial = 16400, (16, 16, 16), (20, 24, 32)
+    g = torch.Generator().manual_seed(8)
+    feat = torch.rand((2, 1) + spatial, generator=g).half()
+    ext = torch.tensor([32.0, 24.0, 20.0])
+    rois = torch.cat([torch.randint(0, 2, (R, 1), generator=g).float(), ext / 2 + (torch.rand(R, 3, generator=g) - 0.5) * 8,
+                      ext * (0.6 + 0.5 * torch.rand(R, 3, generator=g)), (torch.rand(R, 3, generator=g) - 0.5) * 0.8], 1)
+    rois[::2, 7:9] = 0  # every other roi turns about z only
+    rois = rois.half()
+    kw = dict(spatial_scale=1.0, sampling_ratio=1, aligned=True, order=1)
+    out = lib_forward(feat.cuda(), rois.cuda(), out_size, cases.KIND_ROTATED, **kw)
+    pick = torch.cat([torch.arange(0, 40), torch.arange(R - 40, R)])  # the restatement on a sample of the rois
+    oracle = port.forward(feat, rois[pick], out_size, cases.KIND_ROTATED, trig=port.device_trig(rois[pick]), **kw)
+    assert n_mismatch(out[pick], oracle) == 0
+    # and the whole of it against the same call split in two halves that fit the marking launch
+    a = lib_forward(feat.cuda(), rois[:R // 2].cuda(), out_size, cases.KIND_ROTATED, **kw)
+    b = lib_forward(feat.cuda(), rois[R // 2:].cuda(), out_size, cases.KIND_ROTATED, **kw)
+    assert torch.equal(out, torch.cat([a, b]))
