@@ -164,10 +164,24 @@ __device__ __forceinline__ void t3_mbar_arrive_lane0(unsigned bar, int lane) {
       : "memory");
 }
 
+// The rare ways out of the plane-streaming kernel (batch index outside the batch, coordinates that
+// are not finite, a tile whose footprint exceeds every box): the CTA's tile, 16 rows at a time,
+// through the gather path.
+template <typename T>
+__device__ __forceinline__ void t3_fallback(const Params& p, const S3Launch& L, const S3Cta& k, S3Shared<T>& sh, int np) {
+  if (threadIdx.x >= kS3Threads) return;
+  for (int q = 0; q < np; ++q) {
+    S3Cta k2 = k;
+    k2.th = k.th * np + q;
+    if (k2.th * kS3TileH < p.oh) s3_body_l1<T>(p, L, k2, sh);
+  }
+}
+
 // NP = voxel pairs per thread: pair q sits 16*q output rows below pair 0, so a CTA covers a
 // 32 (w) x 16*NP (h) tile.  More work per thread spreads the per-depth control (table read, ring
 // hand-shake, loop) over more voxels.
-template <typename T, int NP>
+// VEC: even output width and aligned pointer, every stored pair is one vector store.
+template <typename T, int NP, bool VEC>
 __global__ void __launch_bounds__(kT3Threads, 3)
 resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constant__ T3Maps maps) {
   typedef Ar<T> A;
@@ -186,26 +200,8 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
   s3_prologue<T>(p, k, sh.s3);  // ends with __syncthreads()
   const RoiGeom<T>& g = sh.s3.g;
   const bool bad_batch = (g.batch < 0 || g.batch >= p.N);
-  if (bad_batch) {  // CTA-uniform: zeros and the status bit, one 16-row sub-tile at a time
-    if (threadIdx.x < kS3Threads) {
-      for (int q = 0; q < NP; ++q) {
-        S3Cta k2 = k;
-        k2.th = k.th * NP + q;
-        if (k2.th * kS3TileH < p.oh) s3_body_l1<T>(p, L, k2, sh.s3);
-      }
-    }
-    return;
-  }
-  if (!sh.s3.zsep) {  // CTA-uniform: general rotation, gathered with plain loads by the consumer warps
-    if (threadIdx.x < kS3Threads) {
-      const int lane_ = threadIdx.x & 31, warp_ = threadIdx.x >> 5;
-      const int pw = k.tw * kS3TileW + (warp_ & 1) * 16 + (lane_ & 7) * 2;
-      const int ph = k.th * (kS3TileH * NP) + (warp_ >> 1) * 4 + (lane_ >> 3);
-      if (pw < p.ow && ph < p.oh) {
-        T* out0 = (T*)p.out + k.nc * p.ovol + (long long)k.pd0 * p.oh * p.ow + (long long)ph * p.ow + pw;
-        s3_full_depth_loop<T, NP>(p, sh.s3, k.npd, k.c, pw, ph, kS3TileH, L.vec_store != 0, out0);
-      }
-    }
+  if (bad_batch || !sh.s3.zsep) {  // CTA-uniform: zeros and the status bit / coordinates that are not finite
+    t3_fallback<T>(p, L, k, sh.s3, NP);
     return;
   }
 
@@ -341,13 +337,7 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
     for (int j = 0; j < maps.n; ++j)
       if (bsel < 0 && need_w <= maps.bw[j] && need_h <= maps.bh[j]) bsel = j;
     if (bsel < 0) {  // the tile's footprint exceeds every box: plain loads
-      if (threadIdx.x < kS3Threads) {
-        for (int q = 0; q < NP; ++q) {
-          S3Cta k2 = k;
-          k2.th = k.th * NP + q;
-          if (k2.th * kS3TileH < p.oh) s3_body_l1<T>(p, L, k2, sh.s3);
-        }
-      }
+      t3_fallback<T>(p, L, k, sh.s3, NP);
       return;
     }
   }
@@ -473,7 +463,7 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
     _Pragma("unroll") for (int q = 0; q < NP; ++q) { STORE }                              \
   }
 
-  if (L.vec_store) {  // even output width and aligned pointer: every stored pair is a vector
+  if (VEC) {
     T3_DEPTH_LOOP(if (act[q]) Q::store2(o + q * sub_o, val[q]);)
   } else {
     T3_DEPTH_LOOP(if (act[q]) { T* oq = o + q * sub_o; oq[0] = Q::lo(val[q]); if (has_b) oq[1] = Q::hi(val[q]); })
@@ -648,12 +638,16 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   cfg.numAttrs = overlap ? 1 : 0;
   cudaError_t err = cudaSuccess;
   // more dynamic shared memory than the default limit: opt in (per function and device)
-#define T3_LAUNCH(TYPE, NP)                                                                                  \
+#define T3_LAUNCH_V(TYPE, NP, VEC)                                                                           \
   {                                                                                                          \
     cfg.dynamicSmemBytes = t3_dynamic_smem<TYPE>(L.ring_bytes);                                              \
-    cudaFuncSetAttribute(resample_fwd_stream3d_tma<TYPE, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                         (int)cfg.dynamicSmemBytes);                                                         \
-    err = cudaLaunchKernelEx(&cfg, resample_fwd_stream3d_tma<TYPE, NP>, p, L, maps);                         \
+    cudaFuncSetAttribute(resample_fwd_stream3d_tma<TYPE, NP, VEC>,                                           \
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes);            \
+    err = cudaLaunchKernelEx(&cfg, resample_fwd_stream3d_tma<TYPE, NP, VEC>, p, L, maps);                    \
+  }
+#define T3_LAUNCH(TYPE, NP)                                                                                  \
+  {                                                                                                          \
+    if (L.vec_store) T3_LAUNCH_V(TYPE, NP, true) else T3_LAUNCH_V(TYPE, NP, false)                           \
   }
   if (dtype == 0) {
     if (pairs == 2) T3_LAUNCH(float, 2) else T3_LAUNCH(float, 1)
@@ -661,6 +655,7 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
     if (pairs == 2) T3_LAUNCH(__half, 2) else T3_LAUNCH(__half, 1)
   }
 #undef T3_LAUNCH
+#undef T3_LAUNCH_V
   if (err != cudaSuccess) return -8;
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
