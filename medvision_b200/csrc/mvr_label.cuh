@@ -77,7 +77,8 @@ resample_label_stream3d(const Params p, const S3Launch L) {
       const int ix = label_axis_pick(rx, p.W, ox), iy = label_axis_pick(ry, p.H, oy);
       off[s] = (ox || oy || ix < 0 || iy < 0 || (s == 1 && !has_b)) ? -1 : iy * p.W + ix;
     }
-    for (int i = 0; i < npd; ++i, out += plane_o) {
+#pragma unroll 4
+    for (int i = 0; i < npd; ++i, out += plane_o) {  // unrolled: several depths' loads in flight
       const S3ZTap<float> e = sh.zt[i];
       int va = 0, vb = 0;
       const bool take0 = e.h == 1.0f, take1 = e.l == 1.0f;
