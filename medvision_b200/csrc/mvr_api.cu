@@ -120,7 +120,7 @@ int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
   }
   if (fwd && try_launch_plane2d(p, dtype, st) == 0)
     return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
-  if (fwd && p.order == 3 && p.ndim == 3) {
+  if (fwd && p.order == 3) {  // Catmull-Rom, 2D and 3D
     int rc;
     switch (dtype) {
       case MVR_F32: rc = launch_cubic3d<float>(p, st); break;

@@ -109,6 +109,86 @@ resample_fwd_cubic3d(const Params p, int ctas_per_roi) {
   }
 }
 
+// 2D counterpart (hermite_2d() of mvr_geom.cuh, interpolation_helpers_2d.h:335-424): u^2 and u^3
+// stay float, the sixteen weights are the doubles wx*wy rounded to the element type, and the
+// sixteen products are ONE left-to-right sum (x fastest) per channel.
+template <typename T, int NC>
+__global__ void __launch_bounds__(kGenericThreads)
+resample_fwd_cubic2d(const Params p, int ctas_per_roi) {
+  typedef Ar<T> A;
+  __shared__ GenericShared<T> sh;
+  const long long n = blockIdx.x / ctas_per_roi;
+  const int first_tile = (int)(blockIdx.x % ctas_per_roi) * kCubicTiles;
+  generic_prologue<T>(p, n, sh);
+  const RoiGeom<T>& g = sh.g;
+  const bool bad = g.batch < 0 || g.batch >= p.N;
+  if (bad && p.status && first_tile == 0 && threadIdx.x == 0) atomicOr(p.status, STATUS_BAD_BATCH_INDEX);
+  const T* vol0 = (const T*)p.in + (long long)(bad ? 0 : g.batch) * p.C * p.vol;
+  const T zero = A::fi(0);
+
+#pragma unroll 1
+  for (int t = 0; t < kCubicTiles; ++t) {
+    const long long e = (long long)(first_tile + t) * kGenericThreads + threadIdx.x;
+    if (e >= p.ovol) return;
+    T* out = (T*)p.out + n * p.C * p.ovol + e;
+    if (bad) {
+      for (int c = 0; c < p.C; ++c) out[c * p.ovol] = zero;
+      continue;
+    }
+    const int pw = (int)(e % p.ow), ph = (int)(e / p.ow);
+    const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], p.fm);
+    const T by = lattice_base<T>(g.start[1], ph, g.bin[1], p.fm);
+#pragma unroll 1
+    for (int c0 = 0; c0 < p.C; c0 += NC) {
+      const T* vc[NC];
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc) vc[cc] = vol0 + (long long)(c0 + cc) * p.vol;
+      T acc[NC];
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc) acc[cc] = zero;
+      for (int iy = 0; iy < g.grid[1]; ++iy) {
+        const T y = A::add(by, sub_offset<T>(sh, 1, iy));
+        for (int ix = 0; ix < g.grid[0]; ++ix) {
+          const T x = A::add(bx, sub_offset<T>(sh, 0, ix));
+          T sx, sy, sz;
+          to_volume<T, 2>(g, p.kind, p.fm, x, y, zero, sx, sy, sz);
+          T val[NC];
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc) val[cc] = zero;
+          if (!(axis_outside<T>(sy, p.H) || axis_outside<T>(sx, p.W))) {
+            int jx[4], jy[4];
+            double wx[4], wy[4];
+            hermite_axis<T, false>(sx, p.W, jx, wx);
+            hermite_axis<T, false>(sy, p.H, jy, wy);
+            T w[16];
+            int o[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int row = jy[j] * p.W;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                w[j * 4 + i] = from_double<T>(__dmul_rn(wx[i], wy[j]));
+                o[j * 4 + i] = row + jx[i];
+              }
+            }
+#pragma unroll
+            for (int cc = 0; cc < NC; ++cc) {
+              T v[16];
+#pragma unroll
+              for (int k = 0; k < 16; ++k) v[k] = __ldg(vc[cc] + o[k]);
+              val[cc] = tap_sum<T, 16>(w, v, p.fm);
+            }
+          }
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc) acc[cc] = A::add(acc[cc], val[cc]);
+        }
+      }
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc) out[(long long)(c0 + cc) * p.ovol] = A::div(acc[cc], g.count_fwd);
+    }
+  }
+}
+
 // 0 launched, 1 not applicable (volume too large for 32-bit tap offsets), -1 too many CTAs
 template <typename T>
 inline int launch_cubic3d(const Params& p, cudaStream_t st) {
@@ -117,6 +197,13 @@ inline int launch_cubic3d(const Params& p, cudaStream_t st) {
   const long long ctas = (long long)p.R * ctas_per_roi;
   if (ctas > 0x7fffffffLL) return -1;
   const unsigned grid = (unsigned)ctas;
+  if (p.ndim == 2) {
+    if (p.C % 4 == 0) resample_fwd_cubic2d<T, 4><<<grid, kGenericThreads, 0, st>>>(p, ctas_per_roi);
+    else if (p.C % 3 == 0) resample_fwd_cubic2d<T, 3><<<grid, kGenericThreads, 0, st>>>(p, ctas_per_roi);
+    else if (p.C % 2 == 0) resample_fwd_cubic2d<T, 2><<<grid, kGenericThreads, 0, st>>>(p, ctas_per_roi);
+    else resample_fwd_cubic2d<T, 1><<<grid, kGenericThreads, 0, st>>>(p, ctas_per_roi);
+    return 0;
+  }
   if (p.C % 4 == 0) resample_fwd_cubic3d<T, 4><<<grid, kGenericThreads, 0, st>>>(p, ctas_per_roi);
   else if (p.C % 3 == 0) resample_fwd_cubic3d<T, 3><<<grid, kGenericThreads, 0, st>>>(p, ctas_per_roi);
   else if (p.C % 2 == 0) resample_fwd_cubic3d<T, 2><<<grid, kGenericThreads, 0, st>>>(p, ctas_per_roi);

@@ -93,10 +93,11 @@ def test_affine_entry_equals_rotated_entry(name, case):
 
 @pytest.mark.parametrize("channels", [1, 2, 4, 5, 8])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
-def test_catmull_rom_3d_channel_groupings(channels, dtype):
-    """The 3D Catmull-Rom kernel carries 1, 2, 3 or 4 channels per pass depending on C; every
+@pytest.mark.parametrize("which", [0, -1], ids=["2d", "3d"])
+def test_catmull_rom_channel_groupings(channels, dtype, which):
+    """The Catmull-Rom kernels carry 1, 2, 3 or 4 channels per pass depending on C; every
     grouping gives what the per-channel restatement gives (and the live reference kernel)."""
-    case = dict(CUBIC[-1][1], C=channels, dtype=dtype, sampling_ratio=1 + channels % 2, seed=900 + channels)
+    case = dict(CUBIC[which][1], C=channels, dtype=dtype, sampling_ratio=1 + channels % 2, seed=900 + channels)
     feat, rois, _ = cases.make_inputs(case)
     out = lib_forward(feat.cuda(), rois.cuda(), case["out_size"], case["kind"], affine=True, **_kw(case))
     oracle = port.forward(feat, rois, case["out_size"], case["kind"], trig=port.device_trig(rois),
