@@ -1,0 +1,108 @@
+"""Randomised sweep over roi kinds, dimensionalities, dtypes, orders, sampling ratios, alignment
+flags, shapes (degenerate ones included) and roi geometries (zero-size rois, rois hanging over the
+border, all rotations).  Forward: bit-identical to the reference's own kernels when they are
+present (else to the CPU restatement).  Backward: float within 1e-4; half -- which the reference
+accumulates with half atomics in arbitrary order, losing up to ~15 % of the maximum under heavy
+up-sampling -- no further from a float32 evaluation than the reference itself is."""
+import math
+import random
+
+import pytest
+import torch
+
+import cases
+from oracle import port, ref
+from util import n_mismatch
+
+pytestmark = pytest.mark.gpu
+REF_FM = 1 | (1 << 1) | (1 << 2) | (1 << 3) | (1 << 5) | (1 << 7) | (1 << 10) | (1 << 13) | \
+    (1 << 16) | (1 << 18) | (2 << 20) | (1 << 22)
+NAMES = {("box", 2): "roi_align_2d", ("box", 3): "roi_align_3d", ("rot", 2): "roi_align_rotated_2d",
+         ("rot", 3): "roi_align_rotated_3d"}
+
+
+def _case(rnd, g):
+    ndim = rnd.choice([2, 3])
+    kind = rnd.choice(["box", "rot"])
+    dt = rnd.choice([torch.float16, torch.float32])
+    order = rnd.choice([0, 1, 1])
+    sr = 1 if order == 0 else rnd.choice([0, 1, 1, 2, 3])
+    aligned = rnd.choice([True, True, False])
+    N, C = rnd.randint(1, 3), rnd.randint(1, 4)
+    big = rnd.random() < 0.5
+    if ndim == 3:
+        spatial = tuple(rnd.randint(1, 40 if big else 12) for _ in range(3))
+        out = tuple(rnd.randint(1, 36 if big else 6) for _ in range(3))
+    else:
+        spatial = tuple(rnd.randint(1, 150 if big else 20) for _ in range(2))
+        out = tuple(rnd.randint(1, 120 if big else 8) for _ in range(2))
+    R = rnd.randint(1, 6)
+    scale = rnd.choice([1.0, 0.5, 0.77])
+    feat = (torch.rand((N, C) + spatial, generator=g) * 2 - 0.5).to(dt)
+    ext = torch.tensor(spatial[::-1], dtype=torch.float32)
+    b = torch.randint(0, N, (R, 1), generator=g).float()
+    centre = ext * torch.rand(R, ndim, generator=g) * 1.2 - 0.1 * ext
+    size = ext * (0.05 + 1.5 * torch.rand(R, ndim, generator=g))
+    if rnd.random() < 0.15:
+        size[0] = 0
+    if kind == "box":
+        rois = torch.cat([b, (centre - size / 2) / scale, (centre + size / 2) / scale], 1)
+    else:
+        ang = (torch.rand(R, 1 if ndim == 2 else 3, generator=g) * 2 - 1) * math.pi
+        mode = rnd.choice(["none", "z", "all"])
+        if mode == "none":
+            ang[:] = 0
+        elif mode == "z" and ndim == 3:
+            ang[:, :2] = 0
+        rois = torch.cat([b, centre / scale, size / scale, ang], 1)
+    return dict(ndim=ndim, kind=kind, dtype=dt, order=order, sr=sr, aligned=aligned, out=out, scale=scale,
+                feat=feat, rois=rois.to(dt))
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_calls_against_the_reference(seed):
+    from medvision_b200 import _C
+    rnd = random.Random(seed)
+    g = torch.Generator().manual_seed(seed)
+    live = ref.module() if ref.available() else None
+    for it in range(100 if live is not None else 25):
+        c = _case(rnd, g)
+        what = "seed %d case %d: %s" % (seed, it, {k: v for k, v in c.items() if k not in ("feat", "rois")})
+        f, r = c["feat"].cuda(), c["rois"].cuda()
+        name = NAMES[(c["kind"], c["ndim"])]
+        extra = (c["aligned"],) if c["kind"] == "rot" else ()
+        shape = (r.size(0), f.size(1)) + c["out"]
+        out = torch.full(shape, float("nan"), dtype=c["dtype"], device="cuda")
+        getattr(_C, name + "_forward")(f, r, out, *c["out"], c["scale"], c["sr"], *extra, c["order"])
+        go = torch.randn(shape, generator=g).to(c["dtype"]).cuda()
+        gin = torch.zeros_like(f)
+        getattr(_C, name + "_backward")(go, r, gin, *c["out"], c["scale"], c["sr"], *extra, c["order"])
+        kind = cases.KIND_BOX if c["kind"] == "box" else cases.KIND_ROTATED
+        kw = dict(spatial_scale=c["scale"], sampling_ratio=c["sr"], aligned=c["aligned"], order=c["order"])
+        if live is not None:
+            want = torch.zeros(shape, dtype=c["dtype"], device="cuda")
+            getattr(live, name + "_forward")(f, r, want, *c["out"], c["scale"], c["sr"], *extra, c["order"])
+            gref = torch.zeros_like(f)
+            getattr(live, name + "_backward")(go, r, gref, *c["out"], c["scale"], c["sr"], *extra, c["order"])
+            torch.cuda.synchronize()
+        else:
+            trig = port.device_trig(c["rois"]) if kind == cases.KIND_ROTATED else None
+            fm = REF_FM if c["dtype"] == torch.float32 else 0
+            want = port.forward(c["feat"], c["rois"], c["out"], kind, trig=trig, fma_mode=fm, **kw)
+            gref = port.backward(go.cpu(), c["rois"], c["feat"].shape, kind, trig=trig, fma_mode=fm, **kw)
+        same_nan = torch.isnan(out).cpu() == torch.isnan(want).cpu()
+        assert bool(same_nan.all()), what
+        assert n_mismatch(torch.nan_to_num(out), torch.nan_to_num(want)) == 0, what
+        if not (bool(torch.isfinite(gref).all()) and bool(torch.isfinite(gin).all())):
+            continue
+        err = float((gin.double().cpu() - gref.double().cpu()).abs().max())
+        top = float(gref.double().abs().max()) + float(gref.double().pow(2).mean().sqrt())
+        if c["dtype"] == torch.float32:
+            assert err <= 1e-4 * top + 1e-12, what
+        elif err > 6e-2 * top + 1e-12:
+            truth = torch.zeros_like(f, dtype=torch.float32)
+            getattr(_C, name + "_backward")(go.float(), r.float(), truth, *c["out"], c["scale"], c["sr"], *extra,
+                                            c["order"])
+            mine = float((gin.float() - truth).abs().max())
+            theirs = float((gref.float().cuda() - truth).abs().max())
+            assert mine <= 2.0 * theirs + 1e-3 * top, what
