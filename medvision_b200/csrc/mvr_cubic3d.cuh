@@ -22,6 +22,7 @@ template <typename T, int NC>
 __global__ void __launch_bounds__(kGenericThreads)
 resample_fwd_cubic3d(const Params p, int ctas_per_roi) {
   typedef Ar<T> A;
+  constexpr int fm = kReferenceContraction;  // the launcher sends other patterns to the general kernel
   __shared__ GenericShared<T> sh;
   const long long n = blockIdx.x / ctas_per_roi;
   const int first_tile = (int)(blockIdx.x % ctas_per_roi) * kCubicTiles;
@@ -45,9 +46,9 @@ resample_fwd_cubic3d(const Params p, int ctas_per_roi) {
     const int pw = (int)(e % p.ow);
     const int ph = (int)((e / p.ow) % p.oh);
     const int pd = (int)(e / ((long long)p.ow * p.oh));
-    const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], p.fm);
-    const T by = lattice_base<T>(g.start[1], ph, g.bin[1], p.fm);
-    const T bz = lattice_base<T>(g.start[2], pd, g.bin[2], p.fm);
+    const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], fm);
+    const T by = lattice_base<T>(g.start[1], ph, g.bin[1], fm);
+    const T bz = lattice_base<T>(g.start[2], pd, g.bin[2], fm);
 
 #pragma unroll 1
     for (int c0 = 0; c0 < p.C; c0 += NC) {
@@ -64,7 +65,7 @@ resample_fwd_cubic3d(const Params p, int ctas_per_roi) {
           for (int ix = 0; ix < g.grid[0]; ++ix) {
             const T x = A::add(bx, sub_offset<T>(sh, 0, ix));
             T sx, sy, sz;
-            to_volume<T, 3>(g, p.kind, p.fm, x, y, z, sx, sy, sz);
+            to_volume<T, 3>(g, p.kind, fm, x, y, z, sx, sy, sz);
             T val[NC];
 #pragma unroll
             for (int cc = 0; cc < NC; ++cc) val[cc] = zero;
@@ -93,7 +94,7 @@ resample_fwd_cubic3d(const Params p, int ctas_per_roi) {
                     T v[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) v[i] = __ldg(vc[cc] + o[i]);
-                    val[cc] = A::add(val[cc], hermite_group4<T>(w, v, p.fm));
+                    val[cc] = A::add(val[cc], hermite_group4<T>(w, v, fm));
                   }
                 }
               }
@@ -116,6 +117,7 @@ template <typename T, int NC>
 __global__ void __launch_bounds__(kGenericThreads)
 resample_fwd_cubic2d(const Params p, int ctas_per_roi) {
   typedef Ar<T> A;
+  constexpr int fm = kReferenceContraction;
   __shared__ GenericShared<T> sh;
   const long long n = blockIdx.x / ctas_per_roi;
   const int first_tile = (int)(blockIdx.x % ctas_per_roi) * kCubicTiles;
@@ -136,8 +138,8 @@ resample_fwd_cubic2d(const Params p, int ctas_per_roi) {
       continue;
     }
     const int pw = (int)(e % p.ow), ph = (int)(e / p.ow);
-    const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], p.fm);
-    const T by = lattice_base<T>(g.start[1], ph, g.bin[1], p.fm);
+    const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], fm);
+    const T by = lattice_base<T>(g.start[1], ph, g.bin[1], fm);
 #pragma unroll 1
     for (int c0 = 0; c0 < p.C; c0 += NC) {
       const T* vc[NC];
@@ -151,7 +153,7 @@ resample_fwd_cubic2d(const Params p, int ctas_per_roi) {
         for (int ix = 0; ix < g.grid[0]; ++ix) {
           const T x = A::add(bx, sub_offset<T>(sh, 0, ix));
           T sx, sy, sz;
-          to_volume<T, 2>(g, p.kind, p.fm, x, y, zero, sx, sy, sz);
+          to_volume<T, 2>(g, p.kind, fm, x, y, zero, sx, sy, sz);
           T val[NC];
 #pragma unroll
           for (int cc = 0; cc < NC; ++cc) val[cc] = zero;
@@ -176,7 +178,7 @@ resample_fwd_cubic2d(const Params p, int ctas_per_roi) {
               T v[16];
 #pragma unroll
               for (int k = 0; k < 16; ++k) v[k] = __ldg(vc[cc] + o[k]);
-              val[cc] = tap_sum<T, 16>(w, v, p.fm);
+              val[cc] = tap_sum<T, 16>(w, v, fm);
             }
           }
 #pragma unroll
@@ -189,10 +191,13 @@ resample_fwd_cubic2d(const Params p, int ctas_per_roi) {
   }
 }
 
-// 0 launched, 1 not applicable (volume too large for 32-bit tap offsets), -1 too many CTAs
+inline int fm_of(const Params& p) { return p.fm; }
+
+// 0 launched, 1 not applicable (volume too large for 32-bit tap offsets, or a float contraction pattern other
+// than the reference build's, which only the debugging switch selects), -1 too many CTAs
 template <typename T>
 inline int launch_cubic3d(const Params& p, cudaStream_t st) {
-  if (p.vol >= 0x7fffffffLL) return 1;
+  if (p.vol >= 0x7fffffffLL || fm_of(p) != kReferenceContraction) return 1;
   const int ctas_per_roi = (p.tiles_per_vol + kCubicTiles - 1) / kCubicTiles;
   const long long ctas = (long long)p.R * ctas_per_roi;
   if (ctas > 0x7fffffffLL) return -1;
