@@ -30,81 +30,16 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PATCH = 96
-
-
-# ----------------------------------------------------------------------------- synthetic data
-def ct_like(shape, seed, device):
-    """int16 CT-like values ~N(-300,400) clipped to [-1024,3071], scaled to [0,1], fp16."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    v = torch.empty(shape, device=device, dtype=torch.float32).normal_(-300, 400, generator=g)
-    v = v.round_().clamp_(-1024, 3071)
-    return ((v + 1024) / 4095).half()
-
-
-def crop_rois(n_vol, per_vol, vol_shape, seed):
-    """rois of CropRandomWithAffine (medvision/aug_cuda_batch/aug_spatial.py:674-715): random
-    patch position, rotation about z within +-20 degrees, scale 0.9-1.1, no shift."""
-    g = torch.Generator().manual_seed(seed)
-    R = n_vol * per_vol
-    D, H, W = vol_shape
-    b = torch.arange(n_vol).repeat_interleave(per_vol).float().view(-1, 1)
-    scale = torch.rand(R, 1, generator=g) * 0.2 + 0.9
-    ext = torch.tensor([W, H, D], dtype=torch.float32)
-    start = torch.rand(R, 3, generator=g) * (ext - PATCH)
-    centre = start + PATCH / 2
-    ang = torch.zeros(R, 3)
-    ang[:, 2] = (torch.rand(R, generator=g) * 2 - 1) * math.radians(20)
-    return torch.cat([b, centre, (PATCH / scale).expand(R, 3), ang], 1)
-
-
-def workload_c5(device, rank, small=False):
-    n_vol, per_vol = (2, 64) if small else (8, 64)
-    shape = (1, 256, 512, 512)
-    vol = ct_like((n_vol,) + shape, 5 + rank, device)
-    rois = crop_rois(n_vol, per_vol, shape[1:], 5 + rank)
-    return dict(name="CropRandomWithAffine %dx(1,256,512,512) fp16 -> (%d,1,96,96,96), z-rotation +-20deg, "
-                     "scale 0.9-1.1" % (n_vol, n_vol * per_vol),
-                features=vol, rois=rois, out_size=(PATCH,) * 3, order=1)
-
-
-def workload_c3(device, rank, small=False):
-    n = 1 if small else 4
-    vol = ct_like((n, 1, 160, 512, 512), 3 + rank, device)
-    rois = torch.tensor([[i, 256, 256, 80, 512, 512, 160, 0, 0, 0] for i in range(n)], dtype=torch.float32)
-    return dict(name="Resize %dx(1,160,512,512) fp16 -> (128,256,256)" % n, features=vol, rois=rois,
-                out_size=(128, 256, 256), order=1)
-
-
-def workload_c4(device, rank, small=False):
-    n = 4 if small else 16
-    g = torch.Generator(device=device).manual_seed(4 + rank)
-    x = torch.empty((n, 1, 128, 128, 128), device=device).normal_(generator=g)
-    k = torch.arange(-12, 13, device=device).float()
-    k = torch.exp(-k * k / 32)
-    k /= k.sum()
-    for d in (2, 3, 4):  # separable Gaussian blur, sigma 4
-        shp = [1, 1, 1, 1, 1]
-        shp[d] = 25
-        pad = [0, 0, 0]
-        pad[d - 2] = 12
-        x = torch.nn.functional.conv3d(x, k.view(shp), padding=pad)
-    x = (x / x.std()).half()
-    gc = torch.Generator().manual_seed(4 + rank)
-    ang = (torch.rand(n, 3, generator=gc) * 2 - 1) * math.radians(30)
-    sc = torch.rand(n, 1, generator=gc) * 0.4 + 0.8
-    sh = (torch.rand(n, 3, generator=gc) * 2 - 1) * 10
-    rois = torch.cat([torch.arange(n).float().view(-1, 1), 64 - sh / sc, (128 / sc).expand(n, 3), ang], 1)
-    return dict(name="RandomAffine (%d,1,128,128,128) fp16, rotation +-30deg x3, scale 0.8-1.2, shift +-10" % n,
-                features=x, rois=rois, out_size=(128, 128, 128), order=1)
-
-
-WORKLOADS = {"c5": workload_c5, "c3": workload_c3, "c4": workload_c4}
+from bench_workloads import (KNOWN_DISTINCT_INPUT_ELEMENTS, PATCH, WORKLOADS, ct_like, workload_c1,  # noqa: E402
+                             workload_c2, workload_c5)
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per output voxel of this library's
 # forward kernel, from one ncu capture of a reduced copy of the workload (profiles/); traffic grows
 # in proportion to the voxels processed, so a launch's traffic is this figure times its outputs.
-DRAM_BYTES_PER_OUTPUT_VOXEL = {"c5": 4.175, "c3": 10.6}
+DRAM_BYTES_PER_OUTPUT_VOXEL = {
+    "c5": {"bytes": 4.175, "source": "profiles/fwd_stream3d_tma_half_c5_small.md (ncu, 2-volume copy of the workload)"},
+    "c3": {"bytes": 10.6, "source": "profiles/fwd_stream3d_tma_half_c3_small.md (ncu, 1-volume copy of the workload)"},
+}
 
 
 # ----------------------------------------------------------------------------- implementations
@@ -116,6 +51,10 @@ class Ours:
         from medvision_b200.ops import affine_3d
         self._C = _C
         self.affine_3d = affine_3d
+
+    def raw(self, name):
+        """the extension function `name` (same names and arguments in both arms)"""
+        return getattr(self._C, name)
 
     def forward_into(self, feat, rois, out, order):
         self._C.affine_3d(feat, rois, out, *out.shape[2:], 1.0, 1, True, order)
@@ -150,6 +89,9 @@ class ReferenceCuda:
     def __init__(self):
         from oracle import ref
         self.m = ref.module()
+
+    def raw(self, name):
+        return getattr(self.m, name)
 
     def forward_into(self, feat, rois, out, order):
         self.m.affine_3d(feat, rois, out, *out.shape[2:], 1.0, 1, True, order)
@@ -294,6 +236,15 @@ def touched_elements(feat, rois, out_size, order):
     return total
 
 
+def distinct_inputs(impl, key, rank, small, feat, rois, out_size, order=1):
+    """U of a workload: counted live by this library's mark kernel in its own arm; the reference arm must load
+    nothing of this library and takes the committed count of the same seeded tensors (None if there is none)."""
+    known = KNOWN_DISTINCT_INPUT_ELEMENTS.get((key, rank, bool(small)))
+    if impl.name != "ours":
+        return known, known
+    return touched_elements(feat, rois, out_size, order), known
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -327,8 +278,9 @@ def cpu_baseline_port(wl, budget_s=15.0):
 def cpu_baseline_torch_function():
     """The reference's torch-function RoIAlign path on CPU (restated in oracle/torch_function_path.py)
     on the RoIAlign 3D head configuration: features (2,4,64,64,64) fp32, 128 rois, output 7^3, forward + backward."""
-    from oracle.torch_function_path import config1_inputs, roi_align_torch_function
-    feat, rois = config1_inputs()
+    from oracle.torch_function_path import roi_align_torch_function
+    w1 = workload_c1()
+    feat, rois = w1["features"], w1["rois"]
     feat.requires_grad_(True)
     g = torch.Generator().manual_seed(2)
     t0 = time.perf_counter()
@@ -341,16 +293,16 @@ def cpu_baseline_torch_function():
             "fwd_bwd": out.numel() / (t2 - t0) / 1e9, "fwd_ms": (t1 - t0) * 1e3, "bwd_ms": (t2 - t1) * 1e3}
 
 
-def detection_configs(impl_name):
-    """Latency of the small detection-style configurations (RoIAlign 3D and RoIAlignRotated 2D heads): forward and
-    forward + backward through the op modules, CUDA events over 200 calls each."""
-    if impl_name != "ours":
-        return None
-    from medvision_b200.ops import RoIAlign, RoIAlignRotated
-    from oracle.torch_function_path import config1_inputs
+def detection_configs(impl):
+    """Latency of the small detection-style configurations (RoIAlign 3D and RoIAlignRotated 2D heads).  Both arms:
+    the two extension calls alone, 200 back-to-back launches between CUDA events (the kernels outlast their launch
+    cost, so this is kernel time).  This library also: the same calls replayed from a CUDA graph (the reference
+    launches on the legacy default stream, which cannot be captured), and forward / forward + backward through the
+    op modules with autograd and Python included."""
     res = []
+    ours = impl.name == "ours"
 
-    def run(name, module, feat, rois, n_out):
+    def run_modules(name, module, feat, rois, n_out):
         feat = feat.cuda().requires_grad_(True)
         rois = rois.cuda().to(feat.dtype)
         out = module(feat, rois)
@@ -365,17 +317,22 @@ def detection_configs(impl_name):
             res.append({"workload": name, "pass": "fwd+bwd" if bwd else "fwd", "us_per_call": ms * 1e3,
                         "gvoxel_per_s": n_out / (ms * 1e-3) / 1e9, "note": "latency-bound; includes autograd and Python"})
 
-    def run_graph(name, fwd_name, bwd_name, feat, rois, out_size, extra):
-        """The two extension calls alone, replayed from a CUDA graph: launch and Python overhead removed."""
-        from medvision_b200 import _C
-        feat = feat.cuda()
-        rois = rois.cuda().to(feat.dtype)
-        out = torch.empty((rois.size(0), feat.size(1)) + tuple(out_size), dtype=feat.dtype, device="cuda")
+    def run_kernels(w, fwd_name, bwd_name, extra):
+        feat = w["features"].cuda()
+        rois = w["rois"].cuda().to(feat.dtype)
+        out_size = tuple(w["out_size"])
+        out = torch.empty((rois.size(0), feat.size(1)) + out_size, dtype=feat.dtype, device="cuda")
         grad = torch.randn_like(out)
         gin = torch.zeros_like(feat)
-        calls = {"fwd": lambda: getattr(_C, fwd_name)(feat, rois, out, *out_size, 1.0, 2, *extra, 1),
-                 "bwd": lambda: getattr(_C, bwd_name)(grad, rois, gin, *out_size, 1.0, 2, *extra, 1)}
+        fwd, bwd = impl.raw(fwd_name), impl.raw(bwd_name)
+        calls = {"fwd": lambda: fwd(feat, rois, out, *out_size, 1.0, w["sampling_ratio"], *extra, 1),
+                 "bwd": lambda: bwd(grad, rois, gin, *out_size, 1.0, w["sampling_ratio"], *extra, 1)}
         for key, call in calls.items():
+            ms = time_steps(call, 200, 20, 1) / 200
+            res.append({"workload": w["name"], "pass": key + " kernel, back-to-back launches", "us_per_call": ms * 1e3,
+                        "gvoxel_per_s": out.numel() / (ms * 1e-3) / 1e9})
+            if not ours:
+                continue
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
                 call()  # first call outside the capture (lazy set-up)
@@ -386,24 +343,19 @@ def detection_configs(impl_name):
                         call()
             torch.cuda.synchronize()
             ms = time_steps(graph.replay, 20, 5, 1) / (20 * 20)
-            res.append({"workload": name, "pass": key + " kernel, CUDA-graph replay", "us_per_call": ms * 1e3,
+            res.append({"workload": w["name"], "pass": key + " kernel, CUDA-graph replay", "us_per_call": ms * 1e3,
                         "gvoxel_per_s": out.numel() / (ms * 1e-3) / 1e9})
 
-    feat, rois = config1_inputs()
-    run_graph("RoIAlign 3D fp32 (2,4,64,64,64), 128 rois, 7x7x7, sampling_ratio 2", "roi_align_3d_forward",
-              "roi_align_3d_backward", feat, rois, (7, 7, 7), ())
-    run("RoIAlign 3D fp32 (2,4,64,64,64), 128 rois, 7x7x7, sampling_ratio 2",
-        RoIAlign((7, 7, 7), 1.0, 2), feat, rois, 128 * 4 * 343)
-    g = torch.Generator().manual_seed(2)
+    w1 = workload_c1()
+    run_kernels(w1, "roi_align_3d_forward", "roi_align_3d_backward", ())
+    if ours:
+        from medvision_b200.ops import RoIAlign, RoIAlignRotated
+        run_modules(w1["name"], RoIAlign((7, 7, 7), 1.0, 2), w1["features"], w1["rois"], 128 * 4 * 343)
     for dt in (torch.float32, torch.float16):
-        f2 = torch.randn(8, 3, 512, 512, generator=g).to(dt)
-        b = torch.randint(0, 8, (512, 1), generator=g).float()
-        r2 = torch.cat([b, torch.rand(512, 2, generator=g) * 512, torch.rand(512, 2, generator=g) * 240 + 16,
-                        (torch.rand(512, 1, generator=g) * 2 - 1) * math.pi], 1)
-        run("RoIAlignRotated 2D %s (8,3,512,512), 512 rois, 14x14, sampling_ratio 2" % str(dt)[6:],
-            RoIAlignRotated((14, 14), 1.0, 2), f2, r2, 512 * 3 * 196)
-        run_graph("RoIAlignRotated 2D %s (8,3,512,512), 512 rois, 14x14, sampling_ratio 2" % str(dt)[6:],
-                  "roi_align_rotated_2d_forward", "roi_align_rotated_2d_backward", f2, r2, (14, 14), (True,))
+        w2 = workload_c2(dtype=dt)
+        run_kernels(w2, "roi_align_rotated_2d_forward", "roi_align_rotated_2d_backward", (True,))
+        if ours:
+            run_modules(w2["name"], RoIAlignRotated((14, 14), 1.0, 2), w2["features"], w2["rois"], 512 * 3 * 196)
     return res
 
 
@@ -450,7 +402,7 @@ def label_config(impl, peak):
     out = impl.label_forward(seg, rois, wl["out_size"])
     ms = time_steps(lambda: impl.label_forward(seg, rois, wl["out_size"]), 20, 5, 1) / 20
     n = out.numel()
-    U = touched_elements(wl["features"], wl["rois"].to(wl["features"].dtype).cuda(), wl["out_size"], 1)
+    U, _ = distinct_inputs(impl, "c5", 0, True, wl["features"], wl["rois"].to(wl["features"].dtype).cuda(), wl["out_size"])
     alg = 4 * n + 4 * U  # int32 result written once; at most the linear path's footprint read once
     return [{"workload": "label crops: 2x(1,256,512,512) int32 -> (128,1,96,96,96) int32, nearest", "pass": "fwd",
              "ms_per_step": ms, "gvoxel_per_s": n / (ms * 1e-3) / 1e9, "algorithmic_bytes": alg,
@@ -536,7 +488,26 @@ def measure_e2e(impl, wl, steps, warmup, world):
     ms = time_steps(step, steps, warmup, world) / steps
     h2d = feat_h.numel() * feat_h.element_size() + rois_h.numel() * rois_h.element_size()
     d2h = out_h.numel() * out_h.element_size()
-    return ms, h2d, d2h, out_h
+
+    # The box's copy ceiling for this step: the same bytes, pinned host <-> device, both directions at
+    # once on two streams, no kernel, every rank at the same time (they share the host's memory and
+    # PCIe paths).  e2e cannot be faster than this; e2e / ceiling says how much of it is overhead.
+    dev_in = torch.empty_like(feat_h, device="cuda")
+    dev_out = torch.empty(out_shape, dtype=feat_h.dtype, device="cuda")
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def copies_only():
+        cur = torch.cuda.current_stream()
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            dev_in.copy_(feat_h, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            out_h.copy_(dev_out, non_blocking=True)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+    ceil_ms = time_steps(copies_only, steps, 2, world) / steps
+    return ms, h2d, d2h, ceil_ms
 
 
 def run_cpu_reference(args, rank):
@@ -549,7 +520,8 @@ def run_cpu_reference(args, rank):
     line = {"impl": "reference", "metric": "resampled Gvoxel/s (fwd)", "value": base["value"], "unit": "Gvoxel/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": wl["name"], "device": "cpu"}, "cpu_baseline": base,
+            "config": {"workload": wl["name"]}, "reference_runs_on": "cpu restatement (oracle/_ref absent)",
+            "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "Gvoxel/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -581,7 +553,7 @@ def main():
     impl = Ours() if args.impl == "ours" else ReferenceCuda()
     if args.workload == "det":
         if rank == 0:
-            print(json.dumps({"impl": args.impl, "detection": detection_configs(args.impl)}))
+            print(json.dumps({"impl": args.impl, "detection": detection_configs(impl)}))
         return
     if args.workload == "elastic":
         if rank == 0:
@@ -611,26 +583,38 @@ def main():
             "gpu_launches": (2 if args.impl == "ours" else 1) * args.steps, "clocks": clocks}
     if args.impl == "reference":
         line["impl"] = "reference"
-        line["config"]["device"] = "cuda: the reference's own kernels, compiled unmodified for sm_100a"
+        line["reference_runs_on"] = "cuda: the reference's own kernels, compiled unmodified for sm_100a"
 
-    # roofline of the dominant (only) kernel: algorithmic bytes / measured launch duration
+    # roofline of the dominant (only) kernel: algorithmic bytes / measured launch duration.  U (distinct
+    # input elements read) is counted by this library's mark kernel in its own arm; the reference arm
+    # loads nothing of this library and takes the committed count of the same seeded workload.
     e = wl["features"].element_size()
     rois_dev = wl["rois"].to(wl["features"].dtype).cuda()
-    U = touched_elements(wl["features"], rois_dev, wl["out_size"], wl["order"])
-    alg_bytes = e * (U + n_out) + rois_dev.numel() * e
+    U, known_u = distinct_inputs(impl, args.workload, rank, args.small, wl["features"], rois_dev, wl["out_size"],
+                                 wl["order"])
     peak, peak_src = load_peaks()
-    achieved = alg_bytes / (ms * 1e-3) / 1e9
-    line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                        "traffic": (DRAM_BYTES_PER_OUTPUT_VOXEL.get(args.workload) * n_out
-                                    if args.impl == "ours" and DRAM_BYTES_PER_OUTPUT_VOXEL.get(args.workload) else None),
-                        "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
-                        "distinct_input_elements": U, "output_elements": n_out,
-                        "frac_of_8000_nominal": achieved / 8000.0}
+    if U is not None:
+        alg_bytes = e * (U + n_out) + rois_dev.numel() * e
+        achieved = alg_bytes / (ms * 1e-3) / 1e9
+        per_voxel = DRAM_BYTES_PER_OUTPUT_VOXEL.get(args.workload) if args.impl == "ours" else None
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                            "traffic": per_voxel["bytes"] * n_out if per_voxel else None,
+                            "traffic_source": per_voxel["source"] if per_voxel else None,
+                            "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
+                            "distinct_input_elements": U, "output_elements": n_out,
+                            "distinct_input_elements_match_committed": (U == known_u) if known_u else None,
+                            "frac_of_8000_nominal": achieved / 8000.0}
 
     if not args.kernel_only:
-        ems, h2d, d2h, _ = measure_e2e(impl, wl, max(2, min(args.steps // 4, 10)), 3, world)
+        ems, h2d, d2h, ceil_ms = measure_e2e(impl, wl, max(2, min(args.steps // 4, 10)), 3, world)
         line["e2e"] = {"value": world * n_out / (ems * 1e-3) / 1e9, "unit": "Gvoxel/s", "ms_per_step": ems,
-                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "h2d_gbs_per_rank": h2d / (ems * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (ems * 1e-3) / 1e9,
+                       "copy_ceiling_ms": ceil_ms, "frac_of_copy_ceiling": ceil_ms / ems,
+                       "copy_ceiling": "the same bytes per step and rank as plain pinned copies in both directions at "
+                                       "once, no kernel, all %d rank(s) together; max over ranks" % world,
+                       "copy_ceiling_h2d_gbs_per_rank": h2d / (ceil_ms * 1e-3) / 1e9,
+                       "copy_ceiling_d2h_gbs_per_rank": d2h / (ceil_ms * 1e-3) / 1e9}
         if args.impl == "reference" and rank == 0:
             line["cpu_baseline"] = {"value": value, "unit": "Gvoxel/s", "cores": 0, "kind": "reference",
                                     "sample": "whole workload on the GPU (the reference path has no CPU implementation)"}
@@ -650,7 +634,7 @@ def main():
                 n2 = w2["rois"].size(0) * math.prod(w2["out_size"])
                 m2, _ = measure(impl, w2, min(max(args.steps, 20), 100), min(args.warmup, 10), 1, backward=bwd)
                 r2 = w2["rois"].to(w2["features"].dtype).cuda()
-                U2 = touched_elements(w2["features"], r2, w2["out_size"], 1)
+                U2, _ = distinct_inputs(impl, key, 0, False, w2["features"], r2, w2["out_size"])
                 b2 = 2 * (U2 + n2) + r2.numel() * 2
                 if bwd:
                     b2 += 2 * (n2 + w2["features"].numel()) + r2.numel() * 2
@@ -661,9 +645,7 @@ def main():
             extra += elastic_config(impl, peak)
             extra += label_config(impl, peak)
             extra += dense2d_config(impl, peak)
-            det = detection_configs(args.impl)
-            if det:
-                extra += det
+            extra += detection_configs(impl)
             line["other_configs"] = extra
     if rank == 0:
         print(json.dumps(line))

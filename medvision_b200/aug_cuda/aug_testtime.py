@@ -1,18 +1,20 @@
 """Sliding-window patch extraction for inference: many rois on one image.
 
-Forward half of ``CudaPatches`` of medvision/aug_cuda/aug_testtime.py:10-150 (anchor grid :44-67,
-roi construction and the ``affine_*`` call :77-150) on a single (C, [D,] H, W) CUDA sample.  The
-detection-box bookkeeping of the reference class (cropBBoxes / padBBoxes / NMS) is not part of the
-resampling path and is not provided.
+``CudaPatches`` of medvision/aug_cuda/aug_testtime.py:10-150 (anchor grid :44-67, roi
+construction and the ``affine_*`` call :77-150) on a single (C, [D,] H, W) CUDA sample.  As in the
+reference, the backward pass only takes the anchor list back out of ``result``
+(aug_testtime.py:69-73): the reference's stitching of image / label patches is commented out
+(:152 onwards) and only its detection boxes are mapped back.  That detection-box bookkeeping
+(cropBBoxes / padBBoxes / NMS) is not part of the resampling path and is not provided.
 """
 import numpy as np
 import torch
 
-from ..aug_cuda_batch.base import BatchCudaAugBase
+from .base import CudaAugBase
 from ..ops.cuda_fun_tools import affine_2d, affine_3d
 
 
-class CudaPatches(BatchCudaAugBase):
+class CudaPatches(CudaAugBase):
     """ONLY FOR INFERENCE OR EVALUATION: cuts the image into overlapping patches.
 
     result['img'] is (C, [D,] H, W); the patches of field ``key`` are stored under
@@ -37,15 +39,6 @@ class CudaPatches(BatchCudaAugBase):
     def canBackward(self):
         return True
 
-    def _init_params(self, result):
-        self.dim = self.dim if self.dim else result['img_dim']
-        self.img_type = result['img'].dtype
-        self.array_shape = tuple(result['img'].shape)
-        self.image_axes = tuple(range(1, self.dim + 1))
-        self.channels = self.array_shape[0]
-        self.image_shape = self.array_shape[1:]
-        self.params = None
-
     def _forward_params(self, result):
         self._init_params(result)
         assert len(self.patch_size) == self.dim
@@ -60,6 +53,12 @@ class CudaPatches(BatchCudaAugBase):
         self.params = anchors
         result[self.key_name] = self.params
 
+    def _backward_params(self, result):
+        self._init_params(result)
+        params = result.pop(self.key_name, None)
+        if params is not None:
+            self.params = np.array(params)
+
     def _rois(self):
         n = len(self.params)
         index = torch.zeros(n, 1)
@@ -70,6 +69,8 @@ class CudaPatches(BatchCudaAugBase):
         return torch.cat([index, center, shape, angles], dim=1)
 
     def apply_to_img(self, result):
+        if not self.isForwarding:
+            return  # nothing is stitched back, as in the reference
         fn = affine_2d if self.dim == 2 else affine_3d
         rois = self._rois()
         for key in result.get('img_fields', []):

@@ -112,6 +112,25 @@ int launch_mark(const Params& p, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
 }
 
+// The kernels that need neither the streaming shape nor any memory beyond inputs and outputs:
+// the flat kernel where it applies, else the one-CTA-per-tile kernel.
+int dispatch_flat_or_generic(const Params& p, int dtype, bool fwd, cudaStream_t st) {
+  {
+    int rc;
+    switch (dtype) {
+      case MVR_F32: rc = launch_flat<float>(p, fwd, st); break;
+      case MVR_F16: rc = launch_flat<__half>(p, fwd, st); break;
+      default: rc = launch_flat<double>(p, fwd, st); break;
+    }
+    if (rc == 0) return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
+  }
+  switch (dtype) {
+    case MVR_F32: return launch_generic<float>(p, fwd, st);
+    case MVR_F16: return launch_generic<__half>(p, fwd, st);
+    default: return launch_generic<double>(p, fwd, st);
+  }
+}
+
 int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
   if (p.R == 0 || p.C == 0) return MVR_OK;
   {
@@ -130,20 +149,7 @@ int dispatch(const Params& p, int dtype, bool fwd, cudaStream_t st) {
     if (rc < 0) return MVR_ERR_TOO_LARGE;
     if (rc == 0) return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
   }
-  {
-    int rc;
-    switch (dtype) {
-      case MVR_F32: rc = launch_flat<float>(p, fwd, st); break;
-      case MVR_F16: rc = launch_flat<__half>(p, fwd, st); break;
-      default: rc = launch_flat<double>(p, fwd, st); break;
-    }
-    if (rc == 0) return cudaGetLastError() == cudaSuccess ? MVR_OK : MVR_ERR_LAUNCH;
-  }
-  switch (dtype) {
-    case MVR_F32: return launch_generic<float>(p, fwd, st);
-    case MVR_F16: return launch_generic<__half>(p, fwd, st);
-    default: return launch_generic<double>(p, fwd, st);
-  }
+  return dispatch_flat_or_generic(p, dtype, fwd, st);
 }
 
 }  // namespace
@@ -247,12 +253,9 @@ int mvr_roi_resample_bwd_noalloc(const void* grad_out, const void* rois, void* g
     if (rc != MVR_OK) return rc;
     return launch_bwd_stream3d_half(p, L, ctas, scratch, st) == 0 ? MVR_OK : MVR_ERR_LAUNCH;
   }
-  // every other shape is served by the element-type-atomics kernel, which has no scratch
-  switch (dtype) {
-    case MVR_F32: return launch_generic<float>(p, false, st);
-    case MVR_F16: return launch_generic<__half>(p, false, st);
-    default: return launch_generic<double>(p, false, st);
-  }
+  // every other shape goes where the regular entry point sends it: kernels that accumulate with
+  // element-type atomics straight into grad_in and use no scratch
+  return dispatch_flat_or_generic(p, dtype, false, st);
 }
 
 static int affine_label_impl(const void* labels, int label_dtype, const float* rois, int32_t* output, int ndim,

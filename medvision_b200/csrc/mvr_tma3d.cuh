@@ -40,6 +40,8 @@ constexpr int kT3MaxPlanes = 2 * kS3MaxChunk;
 constexpr unsigned kT3SpinLimit = 1u << 22;
 constexpr int kT3Threads = kS3Threads + 32;  // 8 consumer warps + 1 producer warp
 constexpr int kT3Pairs = 2;                   // voxel pairs per consumer thread
+constexpr int kT3RingBytes = 60 * 1024;       // plane ring of one CTA: what three resident CTAs per SM can share
+static_assert(kT3RingBytes >= 3 * ((kT3MaxBoxBytes + 127) & ~127), "the ring must hold three of the largest boxes");
 
 struct T3Maps {
   CUtensorMap map[kT3MaxBoxes];  // same tensor (W, H, N*C*D), different box sizes, ascending
@@ -539,15 +541,10 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   if (p.vol >= 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;           // 32-bit offsets inside a volume
   if (dtype == 1 && (p.D > 2048 || p.H > 2048 || p.W > 2048)) return MVR_STREAM3D_NOT_APPLICABLE;  // sizes as half values
 
-  static const bool use_tma = getenv("MVR_NO_TMA") == nullptr;
   T3Maps maps;
-  const bool tma = use_tma && t3_make_maps(p, dtype, maps);
-  static const int env_pairs = getenv("MVR_T3_PAIRS") ? atoi(getenv("MVR_T3_PAIRS")) : 0;
-  const int pairs = (env_pairs == 1 || env_pairs == 2) ? env_pairs : kT3Pairs;
-
+  const bool tma = t3_make_maps(p, dtype, maps);
+  const int pairs = kT3Pairs;
   const size_t esz = dtype == 0 ? 4 : 2;
-  static const int env_chunk = getenv("MVR_T3_CHUNK") ? atoi(getenv("MVR_T3_CHUNK")) : 0;
-  static const int env_ring = getenv("MVR_T3_RING_KB") ? atoi(getenv("MVR_T3_RING_KB")) : 0;
 
   // ---- geometry of the gather kernel (plain loads through L1): 32 x 16 tiles, short depth chunks.
   // Rois under a general rotation are bound by load latency and want many CTAs.  Measured on
@@ -560,7 +557,6 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   {
     int chunk = kS3MaxChunk;
     while (chunk > 8 && g_per_depth * ((p.od + chunk - 1) / chunk) < 148LL * 16) chunk >>= 1;
-    if (env_chunk > 0) chunk = min(env_chunk, kS3MaxChunk);
     G.chunk = min(chunk, p.od);
   }
   G.chunks = (p.od + G.chunk - 1) / G.chunk;
@@ -588,7 +584,6 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
     want = std::max<long long>(want, (p.od + kS3MaxChunk - 1) / kS3MaxChunk);
     want = std::min<long long>(want, std::max(1, p.od / 8));
     int chunk = (int)((p.od + want - 1) / want);
-    if (env_chunk > 0) chunk = min(min(env_chunk, kS3MaxChunk), p.od);
     L.chunk = chunk;
   }
   L.chunks = (p.od + L.chunk - 1) / L.chunk;
@@ -596,7 +591,7 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   const long long ctas = per_depth_ctas * L.chunks;
   if (ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
   // ring of plane boxes: what three resident CTAs per SM can share
-  L.ring_bytes = (env_ring > 0 ? env_ring : 60) * 1024;
+  L.ring_bytes = kT3RingBytes;
   // axis-aligned boxes have no rotation: one launch; rotated rois: this launch takes those that turn
   // about z at most, the gather launch below takes the rest
   const bool two = (p.kind == KIND_ROTATED);
