@@ -77,6 +77,16 @@ int mvr_version(void);
 int mvr_set_float_contraction(int bits);
 int mvr_get_float_contraction(void);
 
+/* Self-test of the bounded waits in the plane-streaming forward kernel; has no counterpart in the
+ * reference.  While `plane` >= 0, the producer of every CTA of that kernel leaves out the plane with
+ * this index of its schedule and all waits get a limit of about a millisecond: the consumers'
+ * wait for that plane runs out, every thread RETURNS (no trap, no endless loop), status bit
+ * MVR_STATUS_TMA_TIMEOUT is set and the output of the call is incomplete.  -1 switches it off.
+ * Process-wide; returns the previous value.  For tests only: it proves that a copy that never
+ * arrives ends in an error status with the context intact. */
+#define MVR_STATUS_TMA_TIMEOUT 2
+int mvr_selftest_tma_skip_plane(int plane);
+
 /* General forward: output[r, c, p] = mean over the roi bin's sub-samples of
  * interp(features[batch(r), c], sample position).
  * Replaces the six forward launchers (medvision/csrc/cuda/roi_align_{2d,3d}_cuda.cu:5-30,

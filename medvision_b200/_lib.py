@@ -14,6 +14,7 @@ MVR_ROI_BOX, MVR_ROI_ROTATED = 0, 1
 MVR_ERR_ROI_WIDTH = -7
 MVR_ERR_UNSUPPORTED = -13
 MVR_STATUS_BAD_BATCH_INDEX = 1
+MVR_STATUS_TMA_TIMEOUT = 2
 
 _i64, _i32, _f32, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -48,7 +49,8 @@ PROTOTYPES = {
     "mvr_affine_2d": _ROT2D,
     "mvr_affine_3d": _ROT3D,
 }
-OTHER_SYMBOLS = ["mvr_strerror", "mvr_version", "mvr_set_float_contraction", "mvr_get_float_contraction"]
+OTHER_SYMBOLS = ["mvr_strerror", "mvr_version", "mvr_set_float_contraction", "mvr_get_float_contraction",
+                 "mvr_selftest_tma_skip_plane"]
 
 
 def _load():
@@ -67,6 +69,8 @@ def _load():
     lib.mvr_set_float_contraction.restype = _i32
     lib.mvr_set_float_contraction.argtypes = [_i32]
     lib.mvr_get_float_contraction.restype = _i32
+    lib.mvr_selftest_tma_skip_plane.restype = _i32
+    lib.mvr_selftest_tma_skip_plane.argtypes = [_i32]
     return lib
 
 

@@ -180,6 +180,8 @@ const char* mvr_strerror(int code) {
 
 int mvr_version(void) { return 1; }
 
+int mvr_selftest_tma_skip_plane(int plane) { return g_t3_selftest_skip_plane.exchange(plane < 0 ? -1 : plane); }
+
 int mvr_set_float_contraction(int bits) { return g_contraction.exchange(bits & 0x00ffffff); }
 int mvr_get_float_contraction(void) { return g_contraction.load(); }
 

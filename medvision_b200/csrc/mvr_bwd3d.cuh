@@ -218,7 +218,6 @@ inline bool bwd_stream3d_applicable(const Params& p, int dtype, S3Launch& L, lon
   L.chunk = chunk;
   L.chunks = (p.od + chunk - 1) / chunk;
   L.vec_store = 0;
-  L.ring_bytes = 0;
   L.filter = 0;
   ctas = per_depth_ctas * L.chunks;
   return ctas <= 0x7fffffffLL;

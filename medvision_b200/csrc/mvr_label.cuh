@@ -194,7 +194,6 @@ inline int launch_label(const Params& p, int label_dtype, cudaStream_t st) {
     L.chunk = min(chunk, p.od);
     L.chunks = (p.od + L.chunk - 1) / L.chunk;
     L.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % 8 == 0);
-    L.ring_bytes = 0;
     L.filter = 0;
     const long long ctas = per_depth * L.chunks;
     if (ctas <= 0x7fffffffLL) {

@@ -199,8 +199,10 @@ struct S3Shared {
 struct S3Launch {
   int tiles_w, tiles_h, chunks, chunk;  // chunk = output depths per CTA
   int vec_store;                        // 1: two-element vector stores are aligned
-  int ring_bytes;                       // TMA-staged kernel: bytes of the shared-memory plane ring
   int filter;                           // 0: every roi; 1: only rois that turn about z at most; 2: only the others
+  // plane-streaming kernel only: limits of its bounded waits, and the self-test's left-out plane (-1: none)
+  int skip_plane = -1;
+  unsigned wait_tries = 1u << 20;       // tries of a bounded wait on a ring slot's barrier (each may be suspended by the hardware)
 };
 
 // General-rotation depth loop for NP voxel pairs of one thread (pair q sits q*row_step output

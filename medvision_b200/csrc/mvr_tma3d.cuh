@@ -26,6 +26,7 @@
 // there is no cluster launch.
 #pragma once
 #include <cuda.h>
+#include <atomic>
 
 #include "mvr_stream3d.cuh"
 
@@ -37,7 +38,6 @@ constexpr int kT3MaxStages = 16;      // ring slots (the ring itself is sized at
 constexpr int kT3MaxBoxBytes = 12800; // largest box; leaves three ring slots
 constexpr int kT3MaxBoxes = 6;
 constexpr int kT3MaxPlanes = 2 * kS3MaxChunk;
-constexpr unsigned kT3SpinLimit = 1u << 22;
 constexpr int kT3Threads = kS3Threads + 32;  // 8 consumer warps + 1 producer warp
 constexpr int kT3Pairs = 2;                   // voxel pairs per consumer thread
 constexpr int kT3RingBytes = 60 * 1024;       // plane ring of one CTA: what three resident CTAs per SM can share
@@ -81,6 +81,8 @@ __device__ __forceinline__ void t3_mbar_expect_tx(unsigned bar, unsigned bytes) 
 __device__ __forceinline__ void t3_mbar_arrive(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One try: the hardware suspends the thread until the phase completes or a system-dependent time limit
+// passes (no issue slots are spent while suspended; in the common case the first try succeeds).
 __device__ __forceinline__ bool t3_mbar_try_wait(unsigned bar, unsigned parity) {
   unsigned ok;
   asm volatile(
@@ -94,13 +96,13 @@ __device__ __forceinline__ bool t3_mbar_try_wait(unsigned bar, unsigned parity) 
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the limit is reached or another thread of the CTA gave up.
-__device__ __forceinline__ bool t3_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+// Bounded wait (producer side): false when `tries` tries did not see the phase complete or another
+// thread of the CTA gave up.
+__device__ __forceinline__ bool t3_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, unsigned tries) {
   if (t3_mbar_try_wait(bar, parity)) return true;
-  for (unsigned spin = 0; spin < kT3SpinLimit; ++spin) {
+  for (unsigned t = 1; t < tries; ++t) {
     if (t3_mbar_try_wait(bar, parity)) return true;
-    if ((spin & 255u) == 255u && abort_flag && *abort_flag) return false;
-    if (spin > 16) __nanosleep(40);
+    if ((t & 63u) == 0 && abort_flag && *abort_flag) return false;
   }
   return false;
 }
@@ -131,10 +133,9 @@ __device__ __forceinline__ Float2Lanes t3_lds_pair<float>(unsigned addr_a, unsig
   return v;
 }
 
-// Bounded wait written as one PTX loop (no divergence bookkeeping around it): up to
-// kT3WaitTries tries, each of which may suspend the thread for up to the time hint.
-constexpr unsigned kT3WaitTries = 1u << 16;
-__device__ __forceinline__ bool t3_mbar_wait_ptx(unsigned bar, unsigned parity) {
+// Bounded wait written as one PTX loop (no divergence bookkeeping around it): up to `tries` tries, each
+// of which the hardware may suspend.
+__device__ __forceinline__ bool t3_mbar_wait_ptx(unsigned bar, unsigned parity, unsigned tries) {
   unsigned ok;
   asm volatile(
       "{\n"
@@ -142,7 +143,7 @@ __device__ __forceinline__ bool t3_mbar_wait_ptx(unsigned bar, unsigned parity) 
       "  .reg .u32 c;\n"
       "  mov.u32 c, 0;\n"
       "T3_WAIT_LOOP:\n"
-      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 20000;\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       "  @p bra T3_WAIT_DONE;\n"
       "  add.u32 c, c, 1;\n"
       "  setp.lt.u32 q, c, %3;\n"
@@ -151,7 +152,7 @@ __device__ __forceinline__ bool t3_mbar_wait_ptx(unsigned bar, unsigned parity) 
       "  selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kT3WaitTries)
+      : "r"(bar), "r"(parity), "r"(tries)
       : "memory");
   return ok != 0;
 }
@@ -184,14 +185,13 @@ __device__ __forceinline__ void t3_fallback(const Params& p, const S3Launch& L, 
 // hand-shake, loop) over more voxels.
 // VEC: even output width and aligned pointer, every stored pair is one vector store.
 template <typename T, int NP, bool VEC>
-__global__ void __launch_bounds__(kT3Threads, 3)
-resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constant__ T3Maps maps) {
+__device__ __forceinline__ void t3_body(const Params& p, const S3Launch& L, const T3Maps& maps) {
   typedef Ar<T> A;
   typedef P2<T> Q;
   typedef typename Q::V V;
   extern __shared__ __align__(128) unsigned char t3_dyn[];
-  unsigned char* ring = t3_dyn;  // L.ring_bytes, 128-byte aligned
-  T3Shared<T>& sh = *reinterpret_cast<T3Shared<T>*>(t3_dyn + L.ring_bytes);
+  unsigned char* ring = t3_dyn;  // kT3RingBytes, 128-byte aligned
+  T3Shared<T>& sh = *reinterpret_cast<T3Shared<T>*>(t3_dyn + kT3RingBytes);
 
   const S3Cta k = s3_cta(p, L);  // k.th counts tiles of 16*NP rows here
   if (s3_filtered_out<T>(p, L, k)) return;
@@ -346,8 +346,10 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
   const int bw = any_inside ? maps.bw[bsel] : 0, bh = any_inside ? maps.bh[bsel] : 0;
   const int n_planes = any_inside ? sh.warp_tot[0] + sh.warp_tot[1] + sh.warp_tot[2] + sh.warp_tot[3] : 0;
   const unsigned box_bytes = (unsigned)(bw * bh * esz);
-  const unsigned stride = (box_bytes + 127u) & ~127u;
-  const int nst = any_inside ? min(kT3MaxStages, (int)(L.ring_bytes / stride)) : 1;
+  // (passed through a warp reduction: the compiler then knows the value is the same in every lane and can keep
+  // slot offsets in uniform registers)
+  const unsigned stride = __reduce_max_sync(0xffffffffu, (box_bytes + 127u) & ~127u);
+  const int nst = any_inside ? min(kT3MaxStages, (int)((unsigned)kT3RingBytes / stride)) : 1;  // >= 4
   const unsigned ring_s = t3_smem(ring);
   const unsigned full_s = t3_smem(&sh.full[0]), empty_s = t3_smem(&sh.empty[0]);
 
@@ -360,10 +362,12 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
     int issued = 0;
     bool ok = true;
     for (; issued < n_planes; ++issued) {
-      ok = t3_mbar_wait(empty_s + 8u * s, par, &sh.abort_flag);
+      ok = t3_mbar_wait(empty_s + 8u * s, par, &sh.abort_flag, L.wait_tries);
       if (!ok) break;
-      t3_mbar_expect_tx(full_s + 8u * s, box_bytes);
-      t3_tma_load_3d(ring_s + s * stride, &maps.map[bsel], full_s + 8u * s, bx0, by0, zbase + sh.plane[issued]);
+      if (issued != L.skip_plane) {  // self-test of the bounded waits: the left-out plane never arrives
+        t3_mbar_expect_tx(full_s + 8u * s, box_bytes);
+        t3_tma_load_3d(ring_s + s * stride, &maps.map[bsel], full_s + 8u * s, bx0, by0, zbase + sh.plane[issued]);
+      }
       if (++s == nst) { s = 0; par ^= 1u; }
     }
     if (!ok) {
@@ -372,7 +376,7 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
       // stay until this CTA's copies in flight have landed (bounded), so that none writes into
       // shared memory that already belongs to another CTA
       for (int j = max(0, issued - nst); j < issued; ++j)
-        t3_mbar_wait(full_s + 8u * (j % nst), (unsigned)((j / nst) & 1), nullptr);
+        if (j != L.skip_plane) t3_mbar_wait(full_s + 8u * (j % nst), (unsigned)((j / nst) & 1), nullptr, L.wait_tries);
     }
     return;
   }
@@ -407,11 +411,12 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
 #pragma unroll
     for (int t = 0; t < 4; ++t) ra[q][t] = rb[q][t] = zero2;
   bool b_newest = true;
+  const unsigned tries = L.wait_tries;
 
 // take the next plane of the schedule out of the ring into register set R
 #define T3_FETCH(R)                                                                       \
   {                                                                                       \
-    if (!t3_mbar_wait_ptx(fa, par)) {                                                     \
+    if (!t3_mbar_wait_ptx(fa, par, tries)) {                                              \
       sh.abort_flag = 1;                                                                  \
       if (p.status && lane == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);                  \
       return; /* no barrier follows: leaving is safe, the producer drains its copies */   \
@@ -475,6 +480,16 @@ resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constan
 #undef T3_FETCH
 }
 
+template <typename T, int NP, bool VEC>
+__global__ void __launch_bounds__(kT3Threads, 3)
+resample_fwd_stream3d_tma(const Params p, const S3Launch L, const __grid_constant__ T3Maps maps) {
+  t3_body<T, NP, VEC>(p, L, maps);
+  // This grid may have been started before the gather launch ahead of it in the stream has finished
+  // (programmatic dependent launch).  One thread waits for that launch before the grid ends, so that
+  // the completion of this grid implies the completion of both, whatever follows in the stream.
+  if (blockIdx.x == 0 && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- host side ---------------------------------------------------------------------------
 
 typedef CUresult (*T3EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -528,7 +543,11 @@ inline bool t3_make_maps(const Params& p, int dtype, T3Maps& m) {
 }
 
 template <typename T>
-inline size_t t3_dynamic_smem(int ring_bytes) { return (size_t)ring_bytes + sizeof(T3Shared<T>); }
+inline size_t t3_dynamic_smem() { return (size_t)kT3RingBytes + sizeof(T3Shared<T>); }
+
+// Self-test hook (mvr_selftest_tma_skip_plane): schedule index of a plane that the producers of the next
+// plane-streaming launches leave out, so that the consumers' bounded waits run out; -1 = off.
+inline std::atomic<int> g_t3_selftest_skip_plane{-1};
 
 // Picks the streaming kernel when the call has its shape; returns MVR_STREAM3D_NOT_APPLICABLE
 // otherwise (the caller then uses the general kernel).
@@ -561,7 +580,6 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   }
   G.chunks = (p.od + G.chunk - 1) / G.chunk;
   G.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % (2 * esz) == 0);
-  G.ring_bytes = 0;
   G.filter = 0;
   const long long g_ctas = g_per_depth * G.chunks;
   if (g_ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
@@ -590,8 +608,8 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   L.vec_store = G.vec_store;
   const long long ctas = per_depth_ctas * L.chunks;
   if (ctas > 0x7fffffffLL) return MVR_STREAM3D_NOT_APPLICABLE;
-  // ring of plane boxes: what three resident CTAs per SM can share
-  L.ring_bytes = kT3RingBytes;
+  L.skip_plane = g_t3_selftest_skip_plane.load();
+  if (L.skip_plane >= 0) L.wait_tries = 32;  // self-test of the bounded waits: short limits
   // axis-aligned boxes have no rotation: one launch; rotated rois: this launch takes those that turn
   // about z at most, the gather launch below takes the rest
   const bool two = (p.kind == KIND_ROTATED);
@@ -635,7 +653,7 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
   // more dynamic shared memory than the default limit: opt in (per function and device)
 #define T3_LAUNCH_V(TYPE, NP, VEC)                                                                           \
   {                                                                                                          \
-    cfg.dynamicSmemBytes = t3_dynamic_smem<TYPE>(L.ring_bytes);                                              \
+    cfg.dynamicSmemBytes = t3_dynamic_smem<TYPE>();                                              \
     cudaFuncSetAttribute(resample_fwd_stream3d_tma<TYPE, NP, VEC>,                                           \
                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes);            \
     err = cudaLaunchKernelEx(&cfg, resample_fwd_stream3d_tma<TYPE, NP, VEC>, p, L, maps);                    \

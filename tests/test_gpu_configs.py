@@ -142,14 +142,15 @@ def test_config4_z_rotation_only_fwd_bwd():
 @needs_reference
 def test_config5_crops_full_size_forward():
     """CropRandomWithAffine 8 x (1,256,512,512) fp16 -> (512,1,96,96,96), forward, full size."""
+    from medvision_b200 import _C
     w = wl.workload_c5("cuda")
     feat, rois = w["features"], w["rois"].half().cuda()
+    _C.last_status()  # clear what earlier tests left in the status word
     out = lib_forward(w, feat, rois, affine=True)
     gold = ref.forward(feat, rois, w["out_size"], w["kind"], affine=True, **ref_kw(w))
     assert out.shape == (512, 1, 96, 96, 96)
     assert mismatches(out, gold) == 0
     # the status word stayed clear (no bounded wait ran out, no bad batch index)
-    from medvision_b200 import _C
     assert _C.last_status() == 0
 
 
