@@ -226,6 +226,19 @@ int mvr_affine_label_3d(const void* labels, int label_dtype, const float* rois, 
                         int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
                         int od, int oh, int ow, float spatial_scale, int aligned, int* status, void* stream);
 
+/* An image field and its label field of one augmentation call in one go; has no counterpart in the
+ * reference, whose transforms call affine_3d twice (medvision/aug_cuda_batch/aug_spatial.py:404-446 for the
+ * image, :451-493 for the label: seg.float() -> affine_3d(order 0) -> .int()).
+ * image / image_rois / image_out: as mvr_affine_3d with sampling_ratio 1 (orders 0, 1); labels / label_rois /
+ * label_out: as mvr_affine_label_3d (label_rois are the same rois in float32).  Results are those of the two
+ * separate calls.  For dense outputs of rotated rois the label's work items ride along with the first of the
+ * image's two overlapped launches, so the pair costs the launches of the image alone; other shapes fall back
+ * to one launch each. */
+int mvr_affine_fields_3d(const void* image, int dtype, const void* image_rois, void* image_out, int64_t C_image,
+                         const void* labels, int label_dtype, const float* label_rois, int32_t* label_out,
+                         int64_t C_label, int64_t N, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od,
+                         int oh, int ow, float spatial_scale, int aligned, int order, int* status, void* stream);
+
 /* ---- elastic warp ---------------------------------------------------------------------- */
 
 /* out[b, c, p] = interp(img[b, c], p + offset[b, :, p]) for every voxel p; float32 / float16;

@@ -215,6 +215,44 @@ def affine_label(input, rois, output, out_sizes, spatial_scale, aligned):
     return True
 
 
+def affine_fields_3d(image, image_rois, image_out, labels, label_rois, label_out, out_sizes, spatial_scale, aligned,
+                     order):
+    """An image field and its label field of one augmentation call: ``affine_3d(image, image_rois, ...,
+    sampling_ratio 1)`` into ``image_out`` and :func:`affine_label` of ``labels`` (float32 ``label_rois``, the same
+    rois) into the int32 ``label_out``, with the label's work riding along with the image's launches where the
+    shapes allow.  Not a function of the reference's extension."""
+    if not (image.is_cuda and labels.is_cuda):
+        raise RuntimeError("RoIAlignRotated is not implemented on CPU")
+    if image.dim() != 5 or labels.dim() != 5 or image.shape[0] != labels.shape[0] or image.shape[2:] != labels.shape[2:]:
+        raise RuntimeError("affine_fields_3d: image and labels must be (N, C, D, H, W) over the same volumes")
+    code = _dtype_code(image, "affine_3d")
+    lcode = _LABEL_DTYPES.get(labels.dtype)
+    if lcode is None or code == _lib.MVR_F64:
+        raise RuntimeError("affine_fields_3d: float16 / float32 image and uint8 / int16 / int32 / int64 labels")
+    for r in (image_rois, label_rois):
+        if r.dim() != 2 or r.size(1) != 10:
+            raise RuntimeError("wrong roi size! size_rois should be 10")
+    R = image_rois.shape[0]
+    if label_rois.shape[0] != R or image_rois.dtype != image.dtype or label_rois.dtype != torch.float32:
+        raise RuntimeError("affine_fields_3d: rois in the image's dtype for the image and in float32 for the labels")
+    dev = image.device
+    for t in (image_rois, image_out, labels, label_rois, label_out):
+        if t.device != dev:
+            raise RuntimeError("expected all tensors to be on the same CUDA device")
+    if image_out.dtype != image.dtype or label_out.dtype != torch.int32:
+        raise RuntimeError("affine_fields_3d: image_out in the image's dtype, label_out int32")
+    if image_out.shape != (R, image.shape[1], *out_sizes) or label_out.shape != (R, labels.shape[1], *out_sizes) \
+            or not image_out.is_contiguous() or not label_out.is_contiguous():
+        raise RuntimeError("affine_fields_3d: the results must be contiguous (R, C, *out_size) tensors")
+    image, labels = image.contiguous(), labels.contiguous()
+    image_rois, label_rois = image_rois.contiguous(), label_rois.contiguous()
+    N, _, D, H, W = image.shape
+    _launch(_FN["mvr_affine_fields_3d"], dev,
+            (image.data_ptr(), code, image_rois.data_ptr(), image_out.data_ptr(), image.shape[1],
+             labels.data_ptr(), lcode, label_rois.data_ptr(), label_out.data_ptr(), labels.shape[1],
+             N, D, H, W, R, 10, *out_sizes, float(spatial_scale), 1 if aligned else 0, int(order), _status_ptr(dev)))
+
+
 def apply_offset(input, offset, order):
     """Displacement-field warp: ``out[b, c, p] = interp(input[b, c], p + offset[b, :, p])``.  Not a
     function of the reference's extension: it is what ``deform_2d`` / ``deform_3d`` compute in the

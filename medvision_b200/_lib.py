@@ -46,6 +46,8 @@ PROTOTYPES = {
     "mvr_affine_label_2d": [_vp, _i32, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _vp],
     "mvr_affine_label_3d": [_vp, _i32, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _f32,
                             _i32, _vp, _vp],
+    "mvr_affine_fields_3d": [_vp, _i32, _vp, _vp, _i64, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32,
+                             _i32, _i32, _i32, _f32, _i32, _i32, _vp, _vp],
     "mvr_affine_2d": _ROT2D,
     "mvr_affine_3d": _ROT3D,
 }

@@ -17,27 +17,52 @@ import numpy as np
 import torch
 
 from .base import BatchCudaAugBase
-from ..ops.cuda_fun_tools import (affine_2d, affine_3d, affine_label_2d, affine_label_3d, apply_offset_2d,
-                                  apply_offset_3d)
+from ..ops.cuda_fun_tools import (affine_2d, affine_3d, affine_fields_3d, affine_label_2d, affine_label_3d,
+                                  apply_offset_2d, apply_offset_3d)
+from ..ops.roi_stage import stage_rois
 
 
 def _resample_fields(result, dim, rois, out_size, sampling_ratio, order):
-    fn = affine_2d if dim == 2 else affine_3d
+    """All image and label fields of ``result`` through the rois of this call (CPU float32).  The rois go to the
+    device once (one asynchronous copy, float32 and float16 at once); in 3D an image field and a label field are
+    resampled by one fused call whose label work rides along with the image's launches."""
     out_size = tuple(int(v) for v in out_size)
-    for key in result.get('img_fields', []):
-        image = result[key]
+    assert not result.get('det_fields'), 'detection boxes are not handled by the resampling transforms'
+    img_keys, seg_keys = list(result.get('img_fields', [])), list(result.get('seg_fields', []))
+    fields = [result[k] for k in img_keys + seg_keys]
+    if not fields:
+        return
+    for image in fields:
         assert image.is_cuda, 'image should be cuda'
         assert image.ndim == dim + 2, 'image should be batch, channel, **dim'
-        result[key] = fn(image, rois.to(image.device, non_blocking=True), out_size, 1.0, sampling_ratio, True, order)
-    for key in result.get('seg_fields', []):
+    device = fields[0].device
+    rois_f32, rois_f16, release = stage_rois(rois, device)
+
+    def rois_for(t):
+        r = rois_f16 if t.dtype == torch.float16 else rois_f32
+        return r if t.device == device else r.to(t.device, non_blocking=True)
+
+    fn = affine_2d if dim == 2 else affine_3d
+    label_fn = affine_label_2d if dim == 2 else affine_label_3d
+    fused = 0
+    if dim == 3 and sampling_ratio == 1 and order in (0, 1):  # pairs of (image field, label field): one call each
+        for ik, sk in zip(img_keys, seg_keys):
+            image, seg = result[ik], result[sk]
+            if image.device != device or seg.device != device or image.shape[0] != seg.shape[0] \
+                    or image.shape[2:] != seg.shape[2:] or image.dtype not in (torch.float16, torch.float32):
+                break
+            result[ik], result[sk] = affine_fields_3d(image, seg, rois_f32, out_size, 1.0, True, order,
+                                                      rois_image=rois_for(image))
+            fused += 1
+    for key in img_keys[fused:]:
         image = result[key]
-        assert image.is_cuda, 'image should be cuda'
-        assert image.ndim == dim + 2, 'image should be batch, channel, **dim'
+        result[key] = fn(image, rois_for(image), out_size, 1.0, sampling_ratio, True, order)
+    for key in seg_keys[fused:]:
+        image = result[key]
         # = fn(image.float(), rois, out_size, 1.0, 1, True, 0).int() of the reference, on the integers themselves
-        label_fn = affine_label_2d if dim == 2 else affine_label_3d
-        result[key] = label_fn(image, rois.to(image.device, non_blocking=True), out_size, 1.0, True)
-    for key in result.get('det_fields', []):
-        raise NotImplementedError
+        r = rois_f32 if image.device == device else rois_f32.to(image.device, non_blocking=True)
+        result[key] = label_fn(image, r, out_size, 1.0, True)
+    release()
 
 
 def _affine_rois(index, center, shape, shifts, scales, rotate, dim):

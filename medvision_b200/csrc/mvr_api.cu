@@ -285,6 +285,37 @@ int mvr_affine_label_3d(const void* labels, int label_dtype, const float* rois, 
                            spatial_scale, aligned, status, stream);
 }
 
+int mvr_affine_fields_3d(const void* image, int dtype, const void* image_rois, void* image_out, int64_t C_image,
+                         const void* labels, int label_dtype, const float* label_rois, int32_t* label_out,
+                         int64_t C_label, int64_t N, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width, int od,
+                         int oh, int ow, float spatial_scale, int aligned, int order, int* status, void* stream) {
+  if (label_dtype < MVR_LABEL_U8 || label_dtype > MVR_LABEL_I64) return MVR_ERR_DTYPE;
+  int rc = check_common(image, image_rois, image_out, dtype, 3, MVR_ROI_ROTATED, N, C_image, D, H, W, R, roi_width, od, oh,
+                        ow, order);
+  if (rc != MVR_OK) return rc;
+  rc = check_common(labels, label_rois, label_out, MVR_F32, 3, MVR_ROI_ROTATED, N, C_label, D, H, W, R, roi_width, od, oh,
+                    ow, 0);
+  if (rc != MVR_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  Params pi = make_params(image, image_rois, image_out, 3, MVR_ROI_ROTATED, N, C_image, D, H, W, R, od, oh, ow,
+                          spatial_scale, 1, aligned, order, status);
+  T3LabelJob job;
+  job.p = make_params(labels, label_rois, label_out, 3, MVR_ROI_ROTATED, N, C_label, D, H, W, R, od, oh, ow, spatial_scale,
+                      1, aligned, 0, status);
+  job.label_dtype = label_dtype;
+  job.done = false;
+  if (pi.R > 0 && pi.C > 0) {
+    int ri = try_launch_stream3d(pi, dtype, st, job.p.C > 0 ? &job : nullptr);
+    if (ri == MVR_STREAM3D_NOT_APPLICABLE) ri = dispatch(pi, dtype, true, st);  // small outputs and the like
+    if (ri != MVR_OK) return ri < 0 && ri != -8 ? ri : MVR_ERR_LAUNCH;
+  }
+  if (!job.done && job.p.R > 0 && job.p.C > 0) {  // the label could not ride along: a launch of its own
+    rc = launch_label(job.p, label_dtype, st);
+    if (rc != 0) return rc == -9 ? MVR_ERR_UNSUPPORTED : MVR_ERR_LAUNCH;
+  }
+  return MVR_OK;
+}
+
 static int apply_offset_impl(const void* img, const void* offset, void* out, int dtype, int offset_dtype, int ndim,
                              int64_t B, int64_t C, int64_t D, int64_t H, int64_t W, int order, void* stream) {
   if (dtype != MVR_F32 && dtype != MVR_F16) return MVR_ERR_DTYPE;

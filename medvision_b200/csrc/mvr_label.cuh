@@ -30,12 +30,10 @@ __device__ __forceinline__ int label_axis_pick(float c, int size, bool& outside)
   return t.h == 1.0f ? t.i0 : (t.l == 1.0f ? t.i1 : -1);
 }
 
+// One work item (32 x 16 tile x depth chunk of one (roi, channel)) of the dense 3D label path.
 template <typename IT>
-__global__ void __launch_bounds__(kS3Threads)
-resample_label_stream3d(const Params p, const S3Launch L) {
+__device__ __forceinline__ void label_item_stream3d(const Params& p, const S3Launch& L, const S3Cta& k, S3Shared<float>& sh) {
   typedef Ar<float> A;
-  __shared__ S3Shared<float> sh;
-  const S3Cta k = s3_cta(p, L);
   s3_prologue<float>(p, k, sh);  // p.order == 0: the per-depth weights in the table are one-hot
   const RoiGeom<float>& g = sh.g;
   const int fm = kS3FloatPattern;
@@ -126,6 +124,50 @@ resample_label_stream3d(const Params p, const S3Launch L) {
   }
 }
 
+template <typename IT>
+__global__ void __launch_bounds__(kS3Threads)
+resample_label_stream3d(const Params p, const S3Launch L) {
+  __shared__ S3Shared<float> sh;
+  label_item_stream3d<IT>(p, L, s3_cta(p, L), sh);
+}
+
+// The gather launch of a rotated forward (resample_fwd_stream3d_rest) with the label field of the same
+// augmentation call riding along: the persistent CTAs first take the image's work items under a general
+// rotation (none for the augmentations, which turn about z only), then stride over the label items.  An
+// image field and its label field thus cost the two overlapped launches of the image alone.
+// p / L / items: the image (element type T); pl / Ll / items_l: the label job (float32 rois, int32 result).
+template <typename T, typename IT>
+__global__ void __launch_bounds__(kS3Threads)
+resample_fwd_stream3d_rest_label(const Params p, const S3Launch L, long long items, const Params pl, const S3Launch Ll,
+                                 long long items_l) {
+  __shared__ union Tables {
+    S3Shared<T> img;
+    S3Shared<float> lab;
+  } sh;
+  __shared__ unsigned general[kS3RestMaxRois / 32];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  int mine = 0;
+  for (int n0 = 0; n0 < p.R; n0 += kS3Threads) {
+    const int n = n0 + threadIdx.x;
+    const bool g = n < p.R && !s3_roi_is_planar<T>(p, n);
+    const unsigned m = __ballot_sync(0xffffffffu, g);
+    if ((threadIdx.x & 31) == 0 && n < kS3RestMaxRois) general[n >> 5] = m;
+    mine |= g;
+  }
+  if (__syncthreads_or(mine))
+    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+      const S3Cta k = s3_cta(p, L, item);
+      if (!((general[k.n >> 5] >> (k.n & 31)) & 1u)) continue;  // CTA-uniform
+      s3_prologue<T>(p, k, sh.img);
+      s3_body_l1<T>(p, L, k, sh.img);
+      __syncthreads();  // the next item's prologue overwrites the tables
+    }
+  for (long long item = blockIdx.x; item < items_l; item += gridDim.x) {
+    label_item_stream3d<IT>(pl, Ll, s3_cta(pl, Ll, item), sh.lab);
+    __syncthreads();
+  }
+}
+
 // 2D labels and small 3D outputs: one thread per output element, every roi decoded per CTA as in
 // the flat kernels.
 template <typename IT, int NDIM>
@@ -180,23 +222,30 @@ resample_label_flat(const Params p, int per_roi) {
 
 enum { LABEL_U8 = 0, LABEL_I16 = 1, LABEL_I32 = 2, LABEL_I64 = 3 };
 
+// Work items of the dense 3D label path; false: the call has not its shape.
+inline bool label_stream3d_geometry(const Params& p, S3Launch& L, long long& items) {
+  if (!(p.ndim == 3 && p.ovol >= 4096 && p.ow >= 8 && p.vol < 0x7fffffffLL && p.fm == kS3FloatPattern)) return false;
+  L.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
+  L.tiles_h = (p.oh + kS3TileH - 1) / kS3TileH;
+  const long long per_depth = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
+  int chunk = kS3MaxChunk;
+  while (chunk > 8 && per_depth * ((p.od + chunk - 1) / chunk) < 148LL * 16) chunk >>= 1;
+  L.chunk = min(chunk, p.od);
+  L.chunks = (p.od + L.chunk - 1) / L.chunk;
+  L.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % 8 == 0);
+  L.filter = 0;
+  items = per_depth * L.chunks;
+  return items <= 0x7fffffffLL;
+}
+
 // p: in = labels, rois = float32 rois, out = int32 result, order = 0, sampling_ratio = 1
 inline int launch_label(const Params& p, int label_dtype, cudaStream_t st) {
   if (p.R == 0 || p.C == 0) return 0;
-  const bool stream3d = p.ndim == 3 && p.ovol >= 4096 && p.ow >= 8 && p.vol < 0x7fffffffLL && p.fm == kS3FloatPattern;
-  if (stream3d) {
-    S3Launch L;
-    L.tiles_w = (p.ow + kS3TileW - 1) / kS3TileW;
-    L.tiles_h = (p.oh + kS3TileH - 1) / kS3TileH;
-    const long long per_depth = (long long)p.R * p.C * L.tiles_w * L.tiles_h;
-    int chunk = kS3MaxChunk;
-    while (chunk > 8 && per_depth * ((p.od + chunk - 1) / chunk) < 148LL * 16) chunk >>= 1;
-    L.chunk = min(chunk, p.od);
-    L.chunks = (p.od + L.chunk - 1) / L.chunk;
-    L.vec_store = ((p.ow & 1) == 0) && (((uintptr_t)p.out) % 8 == 0);
-    L.filter = 0;
-    const long long ctas = per_depth * L.chunks;
-    if (ctas <= 0x7fffffffLL) {
+  S3Launch L;
+  long long items = 0;
+  if (label_stream3d_geometry(p, L, items)) {
+    {
+      const long long ctas = items;
       const unsigned grid = (unsigned)ctas;
       switch (label_dtype) {
         case LABEL_U8: resample_label_stream3d<unsigned char><<<grid, kS3Threads, 0, st>>>(p, L); break;

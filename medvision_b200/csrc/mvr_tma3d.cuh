@@ -28,7 +28,7 @@
 #include <cuda.h>
 #include <atomic>
 
-#include "mvr_stream3d.cuh"
+#include "mvr_label.cuh"
 
 namespace mvr {
 
@@ -549,9 +549,16 @@ inline size_t t3_dynamic_smem() { return (size_t)kT3RingBytes + sizeof(T3Shared<
 // plane-streaming launches leave out, so that the consumers' bounded waits run out; -1 = off.
 inline std::atomic<int> g_t3_selftest_skip_plane{-1};
 
+// A label field to be resampled along with an image (same rois, given in float32; see mvr_label.cuh).
+struct T3LabelJob {
+  Params p;        // in = labels, rois = float32 rois, out = int32 result, order 0, sampling_ratio 1
+  int label_dtype; // LABEL_*
+  bool done;       // set when the label items rode along with the image's gather launch
+};
+
 // Picks the streaming kernel when the call has its shape; returns MVR_STREAM3D_NOT_APPLICABLE
-// otherwise (the caller then uses the general kernel).
-inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
+// otherwise (the caller then uses the general kernel).  `label`: optional label job of the same call.
+inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st, T3LabelJob* label = nullptr) {
   if (p.ndim != 3 || p.sampling_ratio != 1 || p.order > 1) return MVR_STREAM3D_NOT_APPLICABLE;
   if (dtype != 0 /*f32*/ && dtype != 1 /*f16*/) return MVR_STREAM3D_NOT_APPLICABLE;
   if (dtype == 0 && p.fm != kS3FloatPattern) return MVR_STREAM3D_NOT_APPLICABLE;
@@ -629,10 +636,29 @@ inline int try_launch_stream3d(const Params& p, int dtype, cudaStream_t st) {
         else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, resample_fwd_stream3d_rest<__half>, kS3Threads, 0);
         occ[dtype] = n > 0 ? n : 1;
       }
-      const unsigned grid = (unsigned)std::min<long long>(g_ctas, 148LL * occ[dtype]);
       G.filter = 0;
-      if (dtype == 0) resample_fwd_stream3d_rest<float><<<grid, kS3Threads, 0, st>>>(p, G, g_ctas);
-      else resample_fwd_stream3d_rest<__half><<<grid, kS3Threads, 0, st>>>(p, G, g_ctas);
+      S3Launch Ll;
+      long long items_l = 0;
+      if (label && label_stream3d_geometry(label->p, Ll, items_l)) {
+        const unsigned grid = (unsigned)std::min<long long>(std::max(g_ctas, items_l), 148LL * occ[dtype]);
+#define T3_REST_LABEL(TYPE, IT) \
+  resample_fwd_stream3d_rest_label<TYPE, IT><<<grid, kS3Threads, 0, st>>>(p, G, g_ctas, label->p, Ll, items_l)
+#define T3_REST_LABEL_T(TYPE)                                              \
+  switch (label->label_dtype) {                                            \
+    case LABEL_U8: T3_REST_LABEL(TYPE, unsigned char); break;              \
+    case LABEL_I16: T3_REST_LABEL(TYPE, short); break;                     \
+    case LABEL_I32: T3_REST_LABEL(TYPE, int); break;                       \
+    default: T3_REST_LABEL(TYPE, long long); break;                        \
+  }
+        if (dtype == 0) T3_REST_LABEL_T(float) else T3_REST_LABEL_T(__half)
+#undef T3_REST_LABEL_T
+#undef T3_REST_LABEL
+        label->done = true;
+      } else {
+        const unsigned grid = (unsigned)std::min<long long>(g_ctas, 148LL * occ[dtype]);
+        if (dtype == 0) resample_fwd_stream3d_rest<float><<<grid, kS3Threads, 0, st>>>(p, G, g_ctas);
+        else resample_fwd_stream3d_rest<__half><<<grid, kS3Threads, 0, st>>>(p, G, g_ctas);
+      }
       overlap = true;
     } else {
       if (dtype == 0) resample_fwd_stream3d<float><<<(unsigned)g_ctas, kS3Threads, 0, st>>>(p, G);

@@ -74,6 +74,26 @@ def _affine_label(ndim, seg, rois, out_size, spatial_scale, aligned):
     return fn(seg.float(), rois, out_size, spatial_scale, 1, aligned, 0).int()
 
 
+def affine_fields_3d(image, seg, rois, out_size, spatial_scale=1.0, aligned=True, order=1, rois_image=None):
+    """An image field and a label field over the same volumes, resampled with the same rois in one go:
+    returns ``(affine_3d(image, rois, out_size, spatial_scale, 1, aligned, order),
+    affine_label_3d(seg, rois, out_size, spatial_scale, aligned))`` -- what the reference's transforms
+    compute with two ``affine_3d`` calls (medvision/aug_cuda_batch/aug_spatial.py:404-493).
+    ``rois``: float32 (R, 10); ``rois_image``: the same rois already in the image's dtype, if the caller has them."""
+    assert order in [0, 1], f'order {order} is not supported!'
+    out = tuple(int(v) for v in out_size)
+    rois = rois.to(device=image.device, dtype=torch.float32)
+    if rois_image is None:
+        rois_image = rois.to(image.dtype)
+    if seg.dtype not in _C._LABEL_DTYPES or image.dtype not in (torch.float16, torch.float32) or image.dim() != 5:
+        return (affine_3d(image, rois_image, out, spatial_scale, 1, aligned, order),
+                affine_label_3d(seg, rois, out, spatial_scale, aligned))
+    image_out = image.new_empty((rois.shape[0], image.shape[1]) + out)
+    label_out = torch.empty((rois.shape[0], seg.shape[1]) + out, dtype=torch.int32, device=image.device)
+    _C.affine_fields_3d(image, rois_image, image_out, seg, rois, label_out, out, spatial_scale, aligned, order)
+    return image_out, label_out
+
+
 def affine_label_2d(seg, rois, out_size, spatial_scale=1.0, aligned=True):
     """Label map (N, C, H, W) of an integer dtype -> int32 (R, C, oh, ow): what the reference's
     augmentations compute as ``affine_2d(seg.float(), rois, out_size, spatial_scale, 1, aligned,

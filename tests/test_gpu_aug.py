@@ -251,3 +251,54 @@ def test_single_sample_crop_repeats_and_resize_backward():
     back = t(small, forward=False)
     assert back["img"].shape == (1, 16, 32, 32) and back["gt_seg"].shape == (1, 16, 32, 32)
     assert back["history"] == [] and t.key_name not in back
+
+
+def _graph_node_counts(fn):
+    """Capture `fn` into a CUDA graph and count its nodes by kind (kernels, copies)."""
+    from cuda.bindings import runtime as rt
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph(keep_graph=True)
+    with torch.cuda.stream(side):
+        fn()  # lazy set-up (staging buffers, function attributes) outside the capture
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            out = fn()
+    torch.cuda.synchronize()
+    raw = graph.raw_cuda_graph()
+    err, _, n = rt.cudaGraphGetNodes(raw, 0)
+    assert err == rt.cudaError_t.cudaSuccess
+    err, nodes, n = rt.cudaGraphGetNodes(raw, n)
+    kinds = {}
+    for node in nodes[:n]:
+        err, kind = rt.cudaGraphNodeGetType(node)
+        name = getattr(kind, "name", str(kind))
+        kinds[name] = kinds.get(name, 0) + 1
+    graph.instantiate()
+    graph.replay()
+    torch.cuda.synchronize()
+    return kinds, out
+
+
+def test_image_and_label_field_cost_the_launches_of_the_image_alone():
+    """A 3D RandomAffine on an image field and a label field: one asynchronous roi upload and the two overlapped
+    launches a rotated dense forward takes anyway (the label's work rides along with the first) -- no roi cast
+    kernel, no label launch, no float copy of the labels; results bit-equal to the separate calls."""
+    from medvision_b200.aug_cuda_batch import BatchCudaRandomAffine
+    from medvision_b200.ops import affine_3d, affine_label_3d
+    np.random.seed(11)
+    t = BatchCudaRandomAffine(1.0, scale=0.2, shift=0.1, rotate=25)
+    src = _result((2, 1, 32, 48, 64), torch.float16, 5)
+    t(dict(src))  # draws the parameters; the captured calls below reuse them
+    rois = t._rois()
+
+    def both():
+        res = dict(src)
+        t.apply_to_img(res)
+        return res["img"], res["gt_seg"]
+
+    kinds, (img, seg) = _graph_node_counts(both)
+    assert kinds.get("cudaGraphNodeTypeKernel", 0) == 2, kinds
+    assert kinds.get("cudaGraphNodeTypeMemcpy", 0) == 1, kinds
+    want_img = affine_3d(src["img"], rois.cuda(), (32, 48, 64), 1.0, 1, True, 1)
+    want_seg = affine_label_3d(src["gt_seg"], rois.cuda(), (32, 48, 64), 1.0, True)
+    assert torch.equal(img, want_img) and torch.equal(seg, want_seg)
