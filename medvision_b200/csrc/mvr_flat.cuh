@@ -17,7 +17,7 @@
 
 namespace mvr {
 
-constexpr int kFlatThreads = 256;
+constexpr int kFlatThreads = 128;
 constexpr int kFlatMinPerRoi = 32;                                     // outputs per roi (C * ovol) at least
 constexpr int kFlatMaxRois = kFlatThreads / kFlatMinPerRoi + 2;        // rois a CTA can span
 

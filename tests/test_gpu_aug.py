@@ -101,6 +101,18 @@ def test_host_pipeline_equals_one_call():
     got2 = affine_from_host(vol, sorted_rois, (6, 8, 8), 1.0, 1, True, 0)
     want2 = affine_3d(vol.cuda(), sorted_rois.cuda(), (6, 8, 8), 1.0, 1, True, 0).cpu()
     assert torch.equal(got2, want2)
+    # a second call reuses the cached streams and buffers; batch indices outside the batch give zeros, as on
+    # the device; order 3 goes through as well
+    bad = rois.clone()
+    bad[1, 0], bad[6, 0] = -1, 3
+    got3 = affine_from_host(vol, bad, (6, 8, 8), 1.0, 1, True, 1)
+    want3 = affine_3d(vol.cuda(), bad.cuda(), (6, 8, 8), 1.0, 1, True, 1).cpu()
+    assert torch.equal(got3, want3) and torch.count_nonzero(got3[1]) == 0 and torch.count_nonzero(got3[6]) == 0
+    from medvision_b200 import _C
+    _C.last_status()  # the device-side call above flagged the two indices
+    got4 = affine_from_host(vol.float().pin_memory(), rois, (6, 8, 8), 1.0, 1, True, 3)
+    want4 = affine_3d(vol.float().cuda(), rois.cuda(), (6, 8, 8), 1.0, 1, True, 3).cpu()
+    assert torch.equal(got4, want4)
 
 
 def test_sliding_window_patches_are_the_slices():
