@@ -89,3 +89,76 @@ def test_noalloc_backward_refuses_volumes_beyond_its_capacity():
     # the regular entry point takes the same call
     assert _call(L.mvr_roi_resample_bwd, grad, rois, gin) == 0
     torch.cuda.synchronize()
+
+
+def _pool_high_water(reset=False):
+    """High-water mark of the device's default stream-ordered memory pool (the pool the regular entry point
+    borrows its accumulator volume from)."""
+    from cuda.bindings import runtime as rt
+    dev = torch.cuda.current_device()
+    err, pool = rt.cudaDeviceGetDefaultMemPool(dev)
+    assert err == rt.cudaError_t.cudaSuccess
+    if reset:
+        from cuda.bindings.driver import cuuint64_t
+        (err,) = rt.cudaMemPoolSetAttribute(pool, rt.cudaMemPoolAttr.cudaMemPoolAttrUsedMemHigh, cuuint64_t(0))
+        assert err == rt.cudaError_t.cudaSuccess
+    err, used = rt.cudaMemPoolGetAttribute(pool, rt.cudaMemPoolAttr.cudaMemPoolAttrUsedMemHigh)
+    assert err == rt.cudaError_t.cudaSuccess
+    return int(used)
+
+
+def test_noalloc_backward_takes_nothing_from_the_memory_pool():
+    """The regular half backward borrows its accumulator from the device's default memory pool; the variant must
+    leave the pool's high-water mark where it was."""
+    from medvision_b200 import _lib
+    L = _lib.lib
+    grad, rois, shape = _job(505)
+    gin = torch.zeros(shape, dtype=torch.float16, device="cuda")
+    assert _call(L.mvr_roi_resample_bwd_noalloc, grad, rois, gin) == 0  # first call: address look-up done
+    torch.cuda.synchronize()
+    torch.cuda.current_stream().synchronize()
+    before = _pool_high_water(reset=True)
+    assert _call(L.mvr_roi_resample_bwd_noalloc, grad, rois, gin) == 0
+    torch.cuda.synchronize()
+    assert _pool_high_water() == before
+    # ... whereas the regular entry point does borrow from it (the check above can see an allocation)
+    assert _call(L.mvr_roi_resample_bwd, grad, rois, gin) == 0
+    torch.cuda.synchronize()
+    n = 1
+    for s in shape:
+        n *= s
+    assert _pool_high_water() >= before + 4 * n
+
+
+@pytest.mark.parametrize("case", ["head3d_ratio2", "plane2d"])
+def test_noalloc_backward_equals_regular_backward_on_shapes_outside_the_dense_path(case):
+    """Detection-head and 2D shapes need no accumulator volume; both entry points send them to the same kernels
+    (element-type atomics), so the results agree to the order of the atomics."""
+    from medvision_b200 import _lib
+    L = _lib.lib
+    g = torch.Generator().manual_seed(606)
+    if case == "head3d_ratio2":
+        shape, out, R, width, nd, ratio = (2, 3, 16, 20, 24), (5, 6, 7), 9, 10, 3, 2
+        ext = torch.tensor([24., 20., 16.])
+    else:
+        shape, out, R, width, nd, ratio = (2, 3, 1, 40, 48), (1, 9, 11), 7, 6, 2, 1
+        ext = torch.tensor([48., 40.])
+    b = torch.randint(0, 2, (R, 1), generator=g).float()
+    centre = ext / 2 + (torch.rand(R, nd, generator=g) - 0.5) * ext * 0.4
+    size = ext * (0.3 + 0.5 * torch.rand(R, nd, generator=g))
+    ang = (torch.rand(R, 1 if nd == 2 else 3, generator=g) - 0.5) * 0.8
+    rois = torch.cat([b, centre, size, ang], 1).cuda()
+    grad = torch.randn((R, shape[1]) + out, generator=g).cuda()
+    N, C, D, H, W = shape
+
+    def run(fn):
+        gin = torch.zeros(shape, device="cuda")
+        rc = fn(grad.data_ptr(), rois.data_ptr(), gin.data_ptr(), _lib.MVR_F32, nd, _lib.MVR_ROI_ROTATED, N, C, D, H, W,
+                R, width, *out, 1.0, ratio, 1, 1, None, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, _lib.strerror(rc)
+        torch.cuda.synchronize()
+        return gin
+
+    want, got = run(L.mvr_roi_resample_bwd), run(L.mvr_roi_resample_bwd_noalloc)
+    assert float(want.abs().max()) > 0
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-5)
