@@ -99,3 +99,21 @@ def test_output_size_conventions():
         affine_3d(torch.zeros(1, 1, 4, 4, 4, dtype=torch.float64), torch.zeros(1, 10), 2, 1.0)
     m = RoIAlignRotated((2, 3), 0.5, sampling_ratio=2, aligned=False)
     assert (m.dim, m.spatial_scale, m.sampling_ratio, m.aligned) == (2, 0.5, 2, False)
+
+
+def test_build_is_sm_100a_only_and_has_no_fallback_sources():
+    """setup.py / medvision_b200.build: one nvcc call for sm_100a, nothing else (no other architecture, no
+    curand, no Triton, no CPU implementation to fall back to)."""
+    import os
+    from medvision_b200 import build
+    flags = " ".join(build.NVCC_FLAGS)
+    assert "arch=compute_100a,code=sm_100a" in flags
+    assert flags.count("-gencode") == 1 and "curand" not in flags
+    root = os.path.dirname(os.path.dirname(os.path.abspath(build.__file__)))
+    setup_py = open(os.path.join(root, "setup.py")).read()
+    assert "medvision_b200" in setup_py and "build_py" in setup_py and "triton" not in setup_py.lower().replace("no triton", "")
+    for dirpath, _, files in os.walk(os.path.join(root, "medvision_b200")):
+        for f in files:
+            if f.endswith(".py"):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "import triton" not in src and "torch.compile" not in src, f
