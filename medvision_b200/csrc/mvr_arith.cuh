@@ -27,6 +27,8 @@ template <> struct Ar<float> {
   __device__ __forceinline__ static T sub(T a, T b) { return __fsub_rn(a, b); }
   __device__ __forceinline__ static T mul(T a, T b) { return __fmul_rn(a, b); }
   __device__ __forceinline__ static T div(T a, T b) { return __fdiv_rn(a, b); }
+  // a / 2^k written as a * 2^-k (r = 2^-k): the product is exact before its one rounding, so it equals the division
+  __device__ __forceinline__ static T scale_pow2(T a, float r) { return __fmul_rn(a, r); }
   __device__ __forceinline__ static T fma_(T a, T b, T c) { return __fmaf_rn(a, b, c); }
   __device__ __forceinline__ static T neg(T a) { return -a; }
   __device__ __forceinline__ static T fi(int i) { return __int2float_rn(i); }
@@ -50,6 +52,7 @@ template <> struct Ar<double> {
   __device__ __forceinline__ static T sub(T a, T b) { return __dsub_rn(a, b); }
   __device__ __forceinline__ static T mul(T a, T b) { return __dmul_rn(a, b); }
   __device__ __forceinline__ static T div(T a, T b) { return __ddiv_rn(a, b); }
+  __device__ __forceinline__ static T scale_pow2(T a, float r) { return __dmul_rn(a, (double)r); }
   __device__ __forceinline__ static T fma_(T a, T b, T c) { return __fma_rn(a, b, c); }
   __device__ __forceinline__ static T neg(T a) { return -a; }
   __device__ __forceinline__ static T fi(int i) { return (double)i; }
@@ -75,6 +78,8 @@ template <> struct Ar<__half> {
   __device__ __forceinline__ static T div(T a, T b) {
     return __float2half_rn(__fdiv_rn(__half2float(a), __half2float(b)));
   }
+  // the float quotient by 2^k is exact, so the reference's float division + rounding is one rounded half product
+  __device__ __forceinline__ static T scale_pow2(T a, float r) { return __hmul_rn(a, __float2half_rn(r)); }
   __device__ __forceinline__ static T fma_(T a, T b, T c) { return __hadd_rn(__hmul_rn(a, b), c); }  // never fused
   __device__ __forceinline__ static T neg(T a) { return __hneg(a); }
   __device__ __forceinline__ static T fi(int i) { return __float2half_rn(__int2float_rn(i)); }

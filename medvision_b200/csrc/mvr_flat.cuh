@@ -20,40 +20,66 @@ namespace mvr {
 constexpr int kFlatThreads = 128;
 constexpr int kFlatMinPerRoi = 32;                                     // outputs per roi (C * ovol) at least
 constexpr int kFlatMaxRois = kFlatThreads / kFlatMinPerRoi + 2;        // rois a CTA can span
+constexpr int kFlatFm = kS3FloatPattern;                               // float contraction pattern these kernels are built for
+
+// n / d for 0 <= n < 2^31 by one multiplication: m = floor(2^32 (2^s - d) / d) + 1 with s = ceil(log2 d), then
+// q = (hi32(n * m) + n) >> s (the sum cannot carry out of 32 bits because hi32(n * m) <= n < 2^31).
+struct FlatDiv {
+  unsigned d, m, s;
+};
+inline FlatDiv make_flat_div(unsigned d) {
+  FlatDiv f;
+  f.d = d;
+  unsigned s = 0;
+  while ((1ull << s) < d) ++s;
+  f.s = s;
+  f.m = (unsigned)((((1ull << s) - d) << 32) / d + 1);
+  return f;
+}
+__device__ __forceinline__ int flat_div(int n, const FlatDiv& f) {
+  return (int)((__umulhi((unsigned)n, f.m) + (unsigned)n) >> f.s);
+}
+// the four divisors of the flat index: outputs per roi, per channel, per output row and rows per plane
+struct FlatDivs {
+  FlatDiv per_roi, ovol, ow, oh;
+};
 
 // SR: compile-time sampling ratio per axis (1 or 2), or 0 = taken from the roi at run time
 // (any fixed ratio, or the adaptive ceil(bin) grid).
 // OFF: type of the tap offsets inside one channel's volume (int when D*H*W < 2^31).
 template <typename T, int NDIM, int SR, bool BWD, typename OFF>
 __global__ void __launch_bounds__(kFlatThreads)
-resample_flat(const Params p, int per_roi) {
+resample_flat(const Params p, const FlatDivs fd, int total) {
   typedef Ar<T> A;
+  constexpr int fm = kFlatFm;
   __shared__ RoiGeom<T> geo[kFlatMaxRois];
-  const long long total = (long long)p.R * per_roi;
-  const long long e0 = (long long)blockIdx.x * kFlatThreads;
-  const long long n0 = e0 / per_roi;
-  const int rem0 = (int)(e0 - n0 * per_roi);
-  const long long e_last = min(e0 + kFlatThreads, total) - 1;
-  const int n_rois = (int)(e_last / per_roi - n0) + 1;
+  const int per_roi = (int)fd.per_roi.d;
+  const int e0 = (int)blockIdx.x * kFlatThreads;
+  const int n0 = flat_div(e0, fd.per_roi);
+  const int rem0 = e0 - n0 * per_roi;
+  const int e_last = min(e0 + kFlatThreads, total) - 1;
+  const int n_rois = flat_div(e_last, fd.per_roi) - n0 + 1;
   if ((int)threadIdx.x < n_rois) {
     const int osz[3] = {p.ow, p.oh, p.od};
     decode_roi<T>((const T*)p.rois, n0 + threadIdx.x, NDIM, p.kind, osz, p.spatial_scale, p.sampling_ratio, p.aligned,
-                  p.fm, geo[threadIdx.x]);
+                  fm, geo[threadIdx.x]);
   }
   __syncthreads();
-  const long long e = e0 + threadIdx.x;
+  const int e = e0 + (int)threadIdx.x;
   if (e >= total) return;
   const int t = rem0 + (int)threadIdx.x;
-  const int r = t / per_roi;
+  const int r = flat_div(t, fd.per_roi);
   const int rem = t - r * per_roi;
   const RoiGeom<T>& g = geo[r];
-  const int ovol = (int)p.ovol;
-  const int c = rem / ovol;
-  const int v = rem - c * ovol;
-  const int pw = v % p.ow;
-  const int ph = (v / p.ow) % p.oh;
-  const int pd = (NDIM == 3) ? v / (p.ow * p.oh) : 0;
+  const int c = flat_div(rem, fd.ovol);
+  const int v = rem - c * (int)fd.ovol.d;
+  const int row = flat_div(v, fd.ow);                    // (pd * oh + ph)
+  const int pw = v - row * p.ow;
+  const int pd = (NDIM == 3) ? flat_div(row, fd.oh) : 0;
+  const int ph = (NDIM == 3) ? row - pd * p.oh : row;
   const T zero = A::fi(0);
+  // count of samples per output when the sampling ratio is fixed at compile time: a power of two
+  constexpr float inv_count = 1.0f / (float)((SR ? SR : 1) * (SR ? SR : 1) * ((NDIM == 3 && SR) ? SR : 1));
 
   if (g.batch < 0 || g.batch >= p.N) {
     if (p.status && rem == 0) atomicOr(p.status, STATUS_BAD_BATCH_INDEX);
@@ -65,31 +91,34 @@ resample_flat(const Params p, int per_roi) {
   T* gvol = (T*)p.out + ((long long)g.batch * p.C + c) * p.vol;
   const T go = BWD ? ((const T*)p.in)[e] : zero;
 
-  const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], p.fm);
-  const T by = lattice_base<T>(g.start[1], ph, g.bin[1], p.fm);
-  const T bz = (NDIM == 3) ? lattice_base<T>(g.start[2], pd, g.bin[2], p.fm) : zero;
+  const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], fm);
+  const T by = lattice_base<T>(g.start[1], ph, g.bin[1], fm);
+  const T bz = (NDIM == 3) ? lattice_base<T>(g.start[2], pd, g.bin[2], fm) : zero;
   const int gx = SR ? SR : g.grid[0], gy = SR ? SR : g.grid[1], gz = (NDIM == 3) ? (SR ? SR : g.grid[2]) : 1;
 
   T acc = zero;
   auto sample = [&](T x, T y, T z) {
     T sx, sy, sz;
-    to_volume<T, NDIM>(g, p.kind, p.fm, x, y, z, sx, sy, sz);
+    to_volume<T, NDIM>(g, p.kind, fm, x, y, z, sx, sy, sz);
     T w[1 << NDIM];
     OFF off[1 << NDIM];
     const bool in = make_taps<T, NDIM, OFF>(p.D, p.H, p.W, sz, sy, sx, p.order, w, off);
     if (BWD) {
       if (!in) return;
 #pragma unroll
-      for (int k = 0; k < (1 << NDIM); k += 2)
-        atomic_add_pair(gvol + off[k], gvol + off[k + 1], A::div(A::mul(go, w[k]), g.count_bwd),
-                        A::div(A::mul(go, w[k + 1]), g.count_bwd));
+      for (int k = 0; k < (1 << NDIM); k += 2) {
+        // a fixed ratio makes the sample count a power of two: the division is an exact scaling
+        const T g0 = SR ? A::scale_pow2(A::mul(go, w[k]), inv_count) : A::div(A::mul(go, w[k]), g.count_bwd);
+        const T g1 = SR ? A::scale_pow2(A::mul(go, w[k + 1]), inv_count) : A::div(A::mul(go, w[k + 1]), g.count_bwd);
+        atomic_add_pair(gvol + off[k], gvol + off[k + 1], g0, g1);
+      }
     } else {
       T val = zero;
       if (in) {
         T tap[1 << NDIM];
 #pragma unroll
         for (int k = 0; k < (1 << NDIM); ++k) tap[k] = __ldg(vol + off[k]);
-        val = tap_sum<T, (1 << NDIM)>(w, tap, p.fm);
+        val = tap_sum<T, (1 << NDIM)>(w, tap, fm);
       }
       acc = A::add(acc, val);
     }
@@ -100,9 +129,9 @@ resample_flat(const Params p, int per_roi) {
     T subx[S], suby[S], subz[S];
 #pragma unroll
     for (int i = 0; i < S; ++i) {
-      subx[i] = lattice_sub<T>(g.bin[0], i, S);
-      suby[i] = lattice_sub<T>(g.bin[1], i, S);
-      subz[i] = (NDIM == 3) ? lattice_sub<T>(g.bin[2], i, S) : zero;
+      subx[i] = lattice_sub_pow2<T, S>(g.bin[0], i);
+      suby[i] = lattice_sub_pow2<T, S>(g.bin[1], i);
+      subz[i] = (NDIM == 3) ? lattice_sub_pow2<T, S>(g.bin[2], i) : zero;
     }
 #pragma unroll
     for (int iz = 0; iz < ((NDIM == 3) ? S : 1); ++iz) {
@@ -123,7 +152,7 @@ resample_flat(const Params p, int per_roi) {
       }
     }
   }
-  if (!BWD) ((T*)p.out)[e] = A::div(acc, g.count_fwd);
+  if (!BWD) ((T*)p.out)[e] = SR ? A::scale_pow2(acc, inv_count) : A::div(acc, g.count_fwd);
 }
 
 // Forward for axis-aligned boxes (RoIAlign) with a fixed sampling ratio of 1 or 2.  Without a
@@ -133,33 +162,36 @@ resample_flat(const Params p, int per_roi) {
 // reference forms (w = (hz*hy)*hx, left-to-right tap sum); nearest picks per axis, which selects
 // the same tap as the reference's joint first-match rule.
 template <typename T, int NDIM, int SR, typename OFF>
-__global__ void __launch_bounds__(kFlatThreads, 5)
-resample_flat_box_fwd(const Params p, int per_roi) {
+__global__ void __launch_bounds__(kFlatThreads, 10)
+resample_flat_box_fwd(const Params p, const FlatDivs fd, int total) {
   typedef Ar<T> A;
+  constexpr int fm = kFlatFm;
   __shared__ RoiGeom<T> geo[kFlatMaxRois];
-  const long long total = (long long)p.R * per_roi;
-  const long long e0 = (long long)blockIdx.x * kFlatThreads;
-  const long long n0 = e0 / per_roi;
-  const int rem0 = (int)(e0 - n0 * per_roi);
-  const long long e_last = min(e0 + kFlatThreads, total) - 1;
-  const int n_rois = (int)(e_last / per_roi - n0) + 1;
+  const int per_roi = (int)fd.per_roi.d;
+  const int e0 = (int)blockIdx.x * kFlatThreads;
+  const int n0 = flat_div(e0, fd.per_roi);
+  const int rem0 = e0 - n0 * per_roi;
+  const int e_last = min(e0 + kFlatThreads, total) - 1;
+  const int n_rois = flat_div(e_last, fd.per_roi) - n0 + 1;
   if ((int)threadIdx.x < n_rois) {
     const int osz[3] = {p.ow, p.oh, p.od};
-    decode_roi<T>((const T*)p.rois, n0 + threadIdx.x, NDIM, KIND_BOX, osz, p.spatial_scale, SR, p.aligned, p.fm,
+    decode_roi<T>((const T*)p.rois, n0 + threadIdx.x, NDIM, KIND_BOX, osz, p.spatial_scale, SR, p.aligned, fm,
                   geo[threadIdx.x]);
   }
   __syncthreads();
-  const long long e = e0 + threadIdx.x;
+  const int e = e0 + (int)threadIdx.x;
   if (e >= total) return;
   const int t = rem0 + (int)threadIdx.x;
-  const int r = t / per_roi;
+  const int r = flat_div(t, fd.per_roi);
   const int rem = t - r * per_roi;
   const RoiGeom<T>& g = geo[r];
-  const int ovol = (int)p.ovol;
-  const int c = rem / ovol;
-  const int v = rem - c * ovol;
-  const int pos[3] = {v % p.ow, (v / p.ow) % p.oh, (NDIM == 3) ? v / (p.ow * p.oh) : 0};
+  const int c = flat_div(rem, fd.ovol);
+  const int v = rem - c * (int)fd.ovol.d;
+  const int row = flat_div(v, fd.ow);
+  const int pdv = (NDIM == 3) ? flat_div(row, fd.oh) : 0;
+  const int pos[3] = {v - row * p.ow, (NDIM == 3) ? row - pdv * p.oh : row, pdv};
   const T zero = A::fi(0);
+  constexpr float inv_count = 1.0f / (float)(SR * SR * (NDIM == 3 ? SR : 1));
   if (g.batch < 0 || g.batch >= p.N) {
     if (p.status && rem == 0) atomicOr(p.status, STATUS_BAD_BATCH_INDEX);
     ((T*)p.out)[e] = zero;
@@ -175,10 +207,10 @@ resample_flat_box_fwd(const Params p, int per_roi) {
   bool in[NDIM][SR];
 #pragma unroll
   for (int a = 0; a < NDIM; ++a) {
-    const T base = lattice_base<T>(g.start[a], pos[a], g.bin[a], p.fm);
+    const T base = lattice_base<T>(g.start[a], pos[a], g.bin[a], fm);
 #pragma unroll
     for (int i = 0; i < SR; ++i) {
-      const T cc = A::add(base, lattice_sub<T>(g.bin[a], i, SR));
+      const T cc = A::add(base, lattice_sub_pow2<T, SR>(g.bin[a], i));
       in[a][i] = !axis_outside<T>(cc, size[a]);
       AxisTap<T> tp;
       axis_tap<T>(cc, size[a], tp);
@@ -212,7 +244,7 @@ resample_flat_box_fwd(const Params p, int per_roi) {
           const T tap[8] = {__ldg(vol + (b00 + x0)), __ldg(vol + (b00 + x1)), __ldg(vol + (b01 + x0)),
                             __ldg(vol + (b01 + x1)), __ldg(vol + (b10 + x0)), __ldg(vol + (b10 + x1)),
                             __ldg(vol + (b11 + x0)), __ldg(vol + (b11 + x1))};
-          const T sum = tap_sum<T, 8>(w, tap, p.fm);
+          const T sum = tap_sum<T, 8>(w, tap, fm);
           const T val = (in_zy && in[0][ix]) ? sum : zero;
           acc = A::add(acc, val);
         }
@@ -228,33 +260,37 @@ resample_flat_box_fwd(const Params p, int per_roi) {
                         A::mul(wl[1][iy], wh[0][ix]), A::mul(wl[1][iy], wl[0][ix])};
         const T tap[4] = {__ldg(vol + (y0 + x0)), __ldg(vol + (y0 + x1)), __ldg(vol + (y1 + x0)),
                           __ldg(vol + (y1 + x1))};
-        const T sum = tap_sum<T, 4>(w, tap, p.fm);
+        const T sum = tap_sum<T, 4>(w, tap, fm);
         const T val = (in[1][iy] && in[0][ix]) ? sum : zero;
         acc = A::add(acc, val);
       }
     }
   }
-  ((T*)p.out)[e] = A::div(acc, g.count_fwd);
+  ((T*)p.out)[e] = A::scale_pow2(acc, inv_count);
 }
 
 // 0 launched, 1 not applicable
 template <typename T>
 inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
-  if (p.order > 1) return 1;
+  if (p.order > 1 || p.fm != kFlatFm) return 1;
   const long long per_roi = (long long)p.C * p.ovol;
-  if (per_roi < kFlatMinPerRoi || per_roi > (1LL << 30)) return 1;
+  if (per_roi < kFlatMinPerRoi) return 1;
   const long long total = (long long)p.R * per_roi;
-  const long long ctas = (total + kFlatThreads - 1) / kFlatThreads;
-  if (ctas > 0x7fffffffLL) return 1;
-  const unsigned grid = (unsigned)ctas;
-  const int pr = (int)per_roi;
+  if (total + kFlatThreads > 0x7fffffffLL) return 1;  // flat indices (and one CTA beyond) stay below 2^31
+  const unsigned grid = (unsigned)((total + kFlatThreads - 1) / kFlatThreads);
+  FlatDivs fd;
+  fd.per_roi = make_flat_div((unsigned)per_roi);
+  fd.ovol = make_flat_div((unsigned)p.ovol);
+  fd.ow = make_flat_div((unsigned)p.ow);
+  fd.oh = make_flat_div((unsigned)p.oh);
+  const int tot = (int)total;
   const int sr = (p.sampling_ratio == 1 || p.sampling_ratio == 2) ? p.sampling_ratio : 0;
   const bool small = p.vol < 0x7fffffffLL;
   if (fwd && p.kind == KIND_BOX && sr > 0) {
 #define MVR_BOX(ND, SRV)                                                                             \
   {                                                                                                  \
-    if (small) resample_flat_box_fwd<T, ND, SRV, int><<<grid, kFlatThreads, 0, st>>>(p, pr);         \
-    else resample_flat_box_fwd<T, ND, SRV, long long><<<grid, kFlatThreads, 0, st>>>(p, pr);         \
+    if (small) resample_flat_box_fwd<T, ND, SRV, int><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);         \
+    else resample_flat_box_fwd<T, ND, SRV, long long><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);         \
   }
     if (p.ndim == 2) {
       if (sr == 1) MVR_BOX(2, 1) else MVR_BOX(2, 2)
@@ -267,11 +303,11 @@ inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
 #define MVR_FLAT(ND, SRV)                                                                            \
   {                                                                                                  \
     if (small) {                                                                                     \
-      if (fwd) resample_flat<T, ND, SRV, false, int><<<grid, kFlatThreads, 0, st>>>(p, pr);          \
-      else resample_flat<T, ND, SRV, true, int><<<grid, kFlatThreads, 0, st>>>(p, pr);               \
+      if (fwd) resample_flat<T, ND, SRV, false, int><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);          \
+      else resample_flat<T, ND, SRV, true, int><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);               \
     } else {                                                                                         \
-      if (fwd) resample_flat<T, ND, SRV, false, long long><<<grid, kFlatThreads, 0, st>>>(p, pr);    \
-      else resample_flat<T, ND, SRV, true, long long><<<grid, kFlatThreads, 0, st>>>(p, pr);         \
+      if (fwd) resample_flat<T, ND, SRV, false, long long><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);    \
+      else resample_flat<T, ND, SRV, true, long long><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);         \
     }                                                                                                \
   }
   if (p.ndim == 2) {

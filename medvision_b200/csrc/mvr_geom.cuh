@@ -190,24 +190,34 @@ __device__ __forceinline__ void axis_tap(T c, int size, AxisTap<T>& t) {
   t.h = A::sub(A::fi(1), t.l);  // equals the reference's double-precision 1. - l rounded once
 }
 
-template <typename T>
-__device__ __forceinline__ void nearest_pick(const AxisTap<T>* t, int ndim, T* w) {
+// in-bin offset of sub-sample I of a grid of G per axis, G a power of two known at compile time
+template <typename T, int G>
+__device__ __forceinline__ T lattice_sub_pow2(T bin, int i) {
   typedef Ar<T> A;
-  const int nt = 1 << ndim;
-  for (int k = 0; k < nt; ++k) w[k] = A::fi(0);
-  // first tap, in the reference's order, whose per-axis weights are all >= 0.5
-  for (int k = 0; k < nt; ++k) {
-    bool ok = true;
-    for (int a = 0; a < ndim; ++a) {
-      // tap k uses the high weight of axis a when the corresponding bit is clear;
-      // bit order: x is the lowest bit, then y, then z
-      const bool low = (k >> a) & 1;
-      ok = ok && A::ge_half(low ? t[a].l : t[a].h);
-    }
-    if (ok) {
-      w[k] = A::fi(1);
-      break;
-    }
+  static_assert(G == 1 || G == 2 || G == 4, "power of two");
+  const T prod = A::mul(A::ff((float)i + .5f), bin);
+  return (G == 1) ? prod : A::scale_pow2(prod, 1.0f / (float)G);
+}
+
+// order 0: weight 1 for the first tap, in the reference's order, whose per-axis weights are all >= 0.5
+// (tap k uses the high weight of axis a when bit a of k is clear; x is the lowest bit, then y, then z)
+template <typename T, int NDIM>
+__device__ __forceinline__ void nearest_pick(const AxisTap<T>* t, T* w) {
+  typedef Ar<T> A;
+  bool lo[NDIM], hi[NDIM];
+#pragma unroll
+  for (int a = 0; a < NDIM; ++a) {
+    lo[a] = A::ge_half(t[a].l);
+    hi[a] = A::ge_half(t[a].h);
+  }
+  bool found = false;
+#pragma unroll
+  for (int k = 0; k < (1 << NDIM); ++k) {
+    bool ok = !found;
+#pragma unroll
+    for (int a = 0; a < NDIM; ++a) ok = ok && (((k >> a) & 1) ? lo[a] : hi[a]);
+    w[k] = ok ? A::fi(1) : A::fi(0);
+    found = found || ok;
   }
 }
 
@@ -231,7 +241,7 @@ __device__ __forceinline__ bool make_taps(int D, int H, int W, T z, T y, T x, in
     off[2] = y1 + t[0].i0;
     off[3] = y1 + t[0].i1;
     if (order == 0) {
-      nearest_pick<T>(t, 2, w);
+      nearest_pick<T, 2>(t, w);
     } else {
       w[0] = A::mul(t[1].h, t[0].h);
       w[1] = A::mul(t[1].h, t[0].l);
@@ -251,7 +261,7 @@ __device__ __forceinline__ bool make_taps(int D, int H, int W, T z, T y, T x, in
     off[6] = z1 + y1 + t[0].i0;
     off[7] = z1 + y1 + t[0].i1;
     if (order == 0) {
-      nearest_pick<T>(t, 3, w);
+      nearest_pick<T, 3>(t, w);
     } else {
       const T hzhy = A::mul(t[2].h, t[1].h), hzly = A::mul(t[2].h, t[1].l);
       const T lzhy = A::mul(t[2].l, t[1].h), lzly = A::mul(t[2].l, t[1].l);
