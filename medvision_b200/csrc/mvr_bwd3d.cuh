@@ -22,15 +22,9 @@ template <> struct BwdAcc<float> { typedef float type; };
 template <> struct BwdAcc<__half> { typedef float type; };
 
 __device__ __forceinline__ void bwd_red(float* p, float v) { atomicAdd(p, v); }  // result unused: a reduction
-// The two x-neighbours of a tap row are adjacent in memory: when the lower one sits on an 8-byte
-// boundary both go to L2 as one two-element reduction (one operation on one sector instead of two).
-__device__ __forceinline__ void bwd_red_row(float* p0, float* p1, float v0, float v1) {
-  if (p1 == p0 + 1 && (reinterpret_cast<unsigned long long>(p0) & 7ull) == 0) {
-    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p0), "f"(v0), "f"(v1) : "memory");
-  } else {
-    atomicAdd(p0, v0);
-    atomicAdd(p1, v1);
-  }
+// a tap row's two x-neighbours into the float accumulator volume [lo, hi): see atomic_add_pair
+__device__ __forceinline__ void bwd_red_row(float* p0, float* p1, float v0, float v1, const float* lo, const float* hi) {
+  atomic_add_pair(p0, p1, v0, v1, lo, hi);
 }
 
 template <typename T>
@@ -52,18 +46,21 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
     return;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int kStep = 1;  // a thread's two voxels are neighbours along w
   const int pw0 = k.tw * kS3TileW + (warp & 1) * 16 + (lane & 7) * 2;
   const int ph = k.th * kS3TileH + (warp >> 1) * 4 + (lane >> 3);
   if (ph >= p.oh || pw0 >= p.ow) return;
-  const bool has_b = (pw0 + 1 < p.ow);
+  const bool has_b = (pw0 + kStep < p.ow);
   const long long plane_o = (long long)p.oh * p.ow;
   const T* go = (const T*)p.in + k.nc * p.ovol + (long long)k.pd0 * plane_o + (long long)ph * p.ow + pw0;
   Acc* acc = acc_base + ((long long)g.batch * p.C + k.c) * p.vol;
+  const Acc* const acc_lo = acc_base;
+  const Acc* const acc_hi = acc_base + (long long)p.N * p.C * p.vol;
   const long long HW = (long long)p.H * p.W;
 
   const T sub_x = lattice_sub<T>(g.bin[0], 0, 1), sub_y = lattice_sub<T>(g.bin[1], 0, 1);
   const T xa = A::add(lattice_base<T>(g.start[0], pw0, g.bin[0], fm), sub_x);
-  const T xb = A::add(lattice_base<T>(g.start[0], has_b ? pw0 + 1 : pw0, g.bin[0], fm), sub_x);
+  const T xb = A::add(lattice_base<T>(g.start[0], has_b ? pw0 + kStep : pw0, g.bin[0], fm), sub_x);
   const T y = A::add(lattice_base<T>(g.start[1], ph, g.bin[1], fm), sub_y);
   const V x2 = Q::make(xa, xb);
 
@@ -104,19 +101,19 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
       if (plane < 0) return;
       Acc* pl = acc + plane;
       if (ina) {
-        bwd_red_row(pl + oa[0], pl + oa[1], a[0], a[1]);
-        bwd_red_row(pl + oa[2], pl + oa[3], a[2], a[3]);
+        bwd_red_row(pl + oa[0], pl + oa[1], a[0], a[1], acc_lo, acc_hi);
+        bwd_red_row(pl + oa[2], pl + oa[3], a[2], a[3], acc_lo, acc_hi);
       }
       if (inb) {
-        bwd_red_row(pl + ob[0], pl + ob[1], a[4], a[5]);
-        bwd_red_row(pl + ob[2], pl + ob[3], a[6], a[7]);
+        bwd_red_row(pl + ob[0], pl + ob[1], a[4], a[5], acc_lo, acc_hi);
+        bwd_red_row(pl + ob[2], pl + ob[3], a[6], a[7], acc_lo, acc_hi);
       }
     };
     for (int i = 0; i < k.npd; ++i) {
       const S3ZTap<T> e = sh.zt[i];
       if (!e.inside) continue;
       const T ga = go[i * plane_o];
-      const T gb = has_b ? go[i * plane_o + 1] : A::fi(0);
+      const T gb = has_b ? go[i * plane_o + kStep] : A::fi(0);
       const V g2 = Q::make(ga, gb);
       const V hz2 = Q::dup(e.h), lz2 = Q::dup(e.l);
       const V hzhy = Q::mul(hz2, hy2), hzly = Q::mul(hz2, ly2);
@@ -166,7 +163,7 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
     const V ry2 = Q::add(Q::add(sxy[1], Q::dup(e.p[1])), c2[1]);
     const V rz2 = Q::add(Q::add(sxy[2], Q::dup(e.p[2])), c2[2]);
     const T rx[2] = {Q::lo(rx2), Q::hi(rx2)}, ry[2] = {Q::lo(ry2), Q::hi(ry2)}, rz[2] = {Q::lo(rz2), Q::hi(rz2)};
-    const T gv[2] = {go[i * plane_o], has_b ? go[i * plane_o + 1] : A::fi(0)};
+    const T gv[2] = {go[i * plane_o], has_b ? go[i * plane_o + kStep] : A::fi(0)};
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       if (s == 1 && !has_b) continue;
@@ -175,7 +172,8 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
       if (!make_taps<T, 3>(p.D, p.H, p.W, rz[s], ry[s], rx[s], p.order, w, off)) continue;
 #pragma unroll
       for (int t = 0; t < 8; t += 2)
-        bwd_red_row(acc + off[t], acc + off[t + 1], A::tof(A::mul(gv[s], w[t])), A::tof(A::mul(gv[s], w[t + 1])));
+        bwd_red_row(acc + off[t], acc + off[t + 1], A::tof(A::mul(gv[s], w[t])), A::tof(A::mul(gv[s], w[t + 1])), acc_lo,
+                    acc_hi);
     }
   }
   (void)HW;

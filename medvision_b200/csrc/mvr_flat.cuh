@@ -89,6 +89,8 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
   // fwd: the volume read; bwd: the gradient volume accumulated into
   const T* vol = (const T*)(BWD ? p.out : p.in) + ((long long)g.batch * p.C + c) * p.vol;
   T* gvol = (T*)p.out + ((long long)g.batch * p.C + c) * p.vol;
+  const T* const glo = (const T*)p.out;                                // the whole gradient tensor
+  const T* const ghi = glo + (long long)p.N * p.C * p.vol;
   const T go = BWD ? ((const T*)p.in)[e] : zero;
 
   const T bx = lattice_base<T>(g.start[0], pw, g.bin[0], fm);
@@ -110,7 +112,7 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
         // a fixed ratio makes the sample count a power of two: the division is an exact scaling
         const T g0 = SR ? A::scale_pow2(A::mul(go, w[k]), inv_count) : A::div(A::mul(go, w[k]), g.count_bwd);
         const T g1 = SR ? A::scale_pow2(A::mul(go, w[k + 1]), inv_count) : A::div(A::mul(go, w[k + 1]), g.count_bwd);
-        atomic_add_pair(gvol + off[k], gvol + off[k + 1], g0, g1);
+        atomic_add_pair(gvol + off[k], gvol + off[k + 1], g0, g1, glo, ghi);
       }
     } else {
       T val = zero;

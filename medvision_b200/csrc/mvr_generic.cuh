@@ -135,29 +135,66 @@ resample_fwd_generic(const Params p) {
 // element-type atomic add, as the reference's atomicAdd(scalar_t*, scalar_t)
 __device__ __forceinline__ void atomic_add_T(float* p, float v) { atomicAdd(p, v); }
 __device__ __forceinline__ void atomic_add_T(double* p, double v) { atomicAdd(p, v); }
-__device__ __forceinline__ void atomic_add_T(__half* p, __half v) { atomicAdd(p, v); }
+// half: a plain reduction (`atomicAdd(__half*)` asks for the old value back and is several times slower);
+// .noftz keeps subnormals, as the reference's half atomicAdd does
+__device__ __forceinline__ void atomic_add_T(__half* p, __half v) {
+  asm volatile("red.global.add.noftz.f16 [%0], %1;" ::"l"(p), "h"(__half_as_ushort(v)) : "memory");
+}
 
-// The two x-neighbours of a tap row.  When they are adjacent in memory and the lower one is
-// aligned to the pair, both go out as ONE element-type reduction on one L2 sector (float: two
-// 32-bit lanes, half: a packed pair) instead of two; each lane is still an element-type add in
-// whatever order the hardware serves it, as with the reference's scalar atomics.
-__device__ __forceinline__ void atomic_add_pair(float* p0, float* p1, float v0, float v1) {
-  if (p1 == p0 + 1 && (reinterpret_cast<unsigned long long>(p0) & 7ull) == 0) {
-    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p0), "f"(v0), "f"(v1) : "memory");
-  } else {
+// The two x-neighbours of a tap row (p1 == p0 + 1, or p1 == p0 where the upper tap is clamped onto the last
+// column), added to a gradient volume that spans [lo, hi).  Each lane is still an element-type add in whatever
+// order the hardware serves it, as with the reference's scalar atomics.
+//
+// float: the reduction path costs one slot per lane and 16-byte chunk, whatever the width of the operation (and
+// lanes that hit the SAME address do not merge), so a lane sends ONE four-element reduction to the 16-byte window
+// of its lower tap, with the two values in their slots and zeros elsewhere (x + 0 = x); only a lane whose lower tap
+// sits in the window's last slot sends its upper tap separately -- 1.25 operations per row on average.  A window
+// that would reach outside the volume (its first or last elements, when its ends are not 16-byte aligned) is not
+// used: those lanes send two scalar reductions.
+__device__ __forceinline__ void atomic_add_pair(float* p0, float* p1, float v0, float v1, const float* lo,
+                                                const float* hi) {
+  const unsigned k0 = (unsigned)(reinterpret_cast<unsigned long long>(p0) >> 2) & 3u;
+  const unsigned k1 = k0 + (unsigned)(p1 - p0);
+  float* base = p0 - k0;
+  if (base < lo || base + 4 > hi) {
     atomicAdd(p0, v0);
     atomicAdd(p1, v1);
+    return;
   }
+  const float a = (k0 == 0 ? v0 : 0.0f) + (k1 == 0 ? v1 : 0.0f);
+  const float b = (k0 == 1 ? v0 : 0.0f) + (k1 == 1 ? v1 : 0.0f);
+  const float c = (k0 == 2 ? v0 : 0.0f) + (k1 == 2 ? v1 : 0.0f);
+  const float d = (k0 == 3 ? v0 : 0.0f) + (k1 == 3 ? v1 : 0.0f);
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(base), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+  if (k1 == 4) atomicAdd(p1, v1);
 }
-__device__ __forceinline__ void atomic_add_pair(__half* p0, __half* p1, __half v0, __half v1) {
-  if (p1 == p0 + 1 && (reinterpret_cast<unsigned long long>(p0) & 3ull) == 0) {
-    atomicAdd(reinterpret_cast<__half2*>(p0), __halves2half2(v0, v1));
-  } else {
-    atomicAdd(p0, v0);
-    atomicAdd(p1, v1);
+// half: the same with the 16-byte window of eight halves (the upper tap falls outside it one time in eight)
+__device__ __forceinline__ void atomic_add_pair(__half* p0, __half* p1, __half v0, __half v1, const __half* lo,
+                                                const __half* hi) {
+  const unsigned k0 = (unsigned)(reinterpret_cast<unsigned long long>(p0) >> 1) & 7u;
+  __half* base = p0 - k0;
+  if (base < lo || base + 8 > hi) {
+    atomic_add_T(p0, v0);
+    atomic_add_T(p1, v1);
+    return;
   }
+  if (p1 == p0) {  // clamped upper tap: its weight is zero
+    v0 = __hadd_rn(v0, v1);
+    v1 = __ushort_as_half((unsigned short)0);
+  }
+  const unsigned k1 = k0 + 1u;
+  // the two values at halves k0 and k0 + 1 of a 128-bit word
+  const unsigned long long u0 = (unsigned long long)__half_as_ushort(v0) << (16u * (k0 & 3u));
+  const unsigned long long u1 = (k1 < 8u) ? (unsigned long long)__half_as_ushort(v1) << (16u * (k1 & 3u)) : 0ull;
+  const unsigned long long w_lo = (k0 < 4u ? u0 : 0ull) | (k1 < 4u ? u1 : 0ull);
+  const unsigned long long w_hi = (k0 >= 4u ? u0 : 0ull) | (k1 >= 4u ? u1 : 0ull);
+  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(base), "r"((unsigned)w_lo),
+               "r"((unsigned)(w_lo >> 32)), "r"((unsigned)w_hi), "r"((unsigned)(w_hi >> 32))
+               : "memory");
+  if (k1 == 8u && p1 != p0) atomic_add_T(p1, v1);
 }
-__device__ __forceinline__ void atomic_add_pair(double* p0, double* p1, double v0, double v1) {
+__device__ __forceinline__ void atomic_add_pair(double* p0, double* p1, double v0, double v1, const double*,
+                                                const double*) {
   atomicAdd(p0, v0);
   atomicAdd(p1, v1);
 }
