@@ -5,12 +5,15 @@
 // Work is laid out flat, as in the reference (one thread per output element in (roi, channel,
 // [d,] h, w) order), so every thread of a CTA has work whatever the size of a roi's output.  What
 // differs from the reference (medvision/csrc/cuda/roi_align_rotated_3d_cuda_kernel.cuh:15-120 and
-// siblings): the rois a CTA's 256 outputs belong to (at most kFlatMaxRois) are decoded once each,
+// siblings): the rois a CTA's 128 outputs belong to (at most kFlatMaxRois) are decoded once each,
 // by different threads at the same time, into shared memory -- the reference decodes the roi and
 // evaluates up to six sin/cos in every thread, and rebuilds the rotation matrix for every sample;
 // the sample loops of the common fixed sampling ratios (1, 2) are unrolled so that all tap loads
-// of an output are in flight together; offsets are 64-bit.  The arithmetic of every sample is
-// the reference's, operation by operation.
+// of an output are in flight together; the flat index is taken apart with multiply-shift constants
+// from the host instead of divisions; at a fixed sampling ratio the divisions by the sample count
+// and the grid (powers of two) are exact scalings.  Calls with 2^31 outputs or more, or under another
+// float contraction pattern than the reference build's, go to the general kernels.  The arithmetic
+// of every sample is the reference's, operation by operation.
 #pragma once
 #include "mvr_generic.cuh"
 #include "mvr_stream3d.cuh"
