@@ -103,6 +103,9 @@ int mvr_roi_resample_fwd(const void* features, const void* rois, void* output, i
  * medvision/ops/roi_align_rotated_nd.py:148) and is accumulated into, like the reference
  * (medvision/csrc/cuda/roi_align_rotated_3d_cuda_kernel.cuh:251-260): with atomics in the element
  * type, except that half gradients of dense 3D calls are summed in float and rounded once.
+ * The two x-neighbours of a tap row are added by one 16-byte reduction that carries zeros in its
+ * other slots, so elements of grad_in next to a tap may have +0 added to them (a -0 becomes +0);
+ * nothing outside the N*C*D*H*W elements of grad_in is touched.
  * Replaces the four backward launchers (medvision/csrc/cuda/roi_align*_cuda.cu:32-55). */
 int mvr_roi_resample_bwd(const void* grad_out, const void* rois, void* grad_in, int dtype, int ndim, int roi_kind,
                          int64_t N, int64_t C, int64_t D, int64_t H, int64_t W, int64_t R, int roi_width,
