@@ -47,6 +47,16 @@ struct FlatDivs {
   FlatDiv per_roi, ovol, ow, oh;
 };
 
+// These kernels run for 10-30 us, of which the boundary between two launches on a stream is 2 us: they are launched
+// as programmatic dependents, so that the CTAs of a call can become resident while the last CTAs of the call before
+// it are still running.  Every kernel waits (griddepcontrol.wait) for the complete end of whatever precedes it in the
+// stream before it touches memory, and lets its own dependents be scheduled from then on.  After a kernel that
+// never signals (any kernel that is not one of these) the launch behaves like a plain one.
+__device__ __forceinline__ void flat_grid_dependency() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // SR: compile-time sampling ratio per axis (1 or 2), or 0 = taken from the roi at run time
 // (any fixed ratio, or the adaptive ceil(bin) grid).
 // OFF: type of the tap offsets inside one channel's volume (int when D*H*W < 2^31).
@@ -57,6 +67,7 @@ __global__ void __launch_bounds__(kFlatThreads, (NDIM == 2 && BWD && sizeof(T) =
 resample_flat(const Params p, const FlatDivs fd, int total) {
   typedef Ar<T> A;
   constexpr int fm = kFlatFm;
+  flat_grid_dependency();
   __shared__ RoiGeom<T> geo[kFlatMaxRois];
   const int per_roi = (int)fd.per_roi.d;
   const int e0 = (int)blockIdx.x * kFlatThreads;
@@ -173,6 +184,7 @@ __global__ void __launch_bounds__(kFlatThreads, 10)
 resample_flat_box_fwd(const Params p, const FlatDivs fd, int total) {
   typedef Ar<T> A;
   constexpr int fm = kFlatFm;
+  flat_grid_dependency();
   __shared__ RoiGeom<T> geo[kFlatMaxRois];
   const int per_roi = (int)fd.per_roi.d;
   const int e0 = (int)blockIdx.x * kFlatThreads;
@@ -276,6 +288,20 @@ resample_flat_box_fwd(const Params p, const FlatDivs fd, int total) {
   ((T*)p.out)[e] = A::scale_pow2(acc, inv_count);
 }
 
+template <typename K>
+inline void flat_launch(K kernel, unsigned grid, cudaStream_t st, const Params& p, const FlatDivs& fd, int total) {
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kFlatThreads);
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, p, fd, total);
+}
+
 // 0 launched, 1 not applicable
 template <typename T>
 inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
@@ -296,8 +322,8 @@ inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
   if (fwd && p.kind == KIND_BOX && sr > 0) {
 #define MVR_BOX(ND, SRV)                                                                             \
   {                                                                                                  \
-    if (small) resample_flat_box_fwd<T, ND, SRV, int><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);         \
-    else resample_flat_box_fwd<T, ND, SRV, long long><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);         \
+    if (small) flat_launch(resample_flat_box_fwd<T, ND, SRV, int>, grid, st, p, fd, tot);         \
+    else flat_launch(resample_flat_box_fwd<T, ND, SRV, long long>, grid, st, p, fd, tot);         \
   }
     if (p.ndim == 2) {
       if (sr == 1) MVR_BOX(2, 1) else MVR_BOX(2, 2)
@@ -310,11 +336,11 @@ inline int launch_flat(const Params& p, bool fwd, cudaStream_t st) {
 #define MVR_FLAT(ND, SRV)                                                                            \
   {                                                                                                  \
     if (small) {                                                                                     \
-      if (fwd) resample_flat<T, ND, SRV, false, int><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);          \
-      else resample_flat<T, ND, SRV, true, int><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);               \
+      if (fwd) flat_launch(resample_flat<T, ND, SRV, false, int>, grid, st, p, fd, tot);          \
+      else flat_launch(resample_flat<T, ND, SRV, true, int>, grid, st, p, fd, tot);               \
     } else {                                                                                         \
-      if (fwd) resample_flat<T, ND, SRV, false, long long><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);    \
-      else resample_flat<T, ND, SRV, true, long long><<<grid, kFlatThreads, 0, st>>>(p, fd, tot);         \
+      if (fwd) flat_launch(resample_flat<T, ND, SRV, false, long long>, grid, st, p, fd, tot);    \
+      else flat_launch(resample_flat<T, ND, SRV, true, long long>, grid, st, p, fd, tot);         \
     }                                                                                                \
   }
   if (p.ndim == 2) {

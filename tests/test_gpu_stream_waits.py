@@ -80,3 +80,49 @@ def test_results_of_both_forward_launches_are_visible_to_what_follows(rot):
     torch.cuda.synchronize()
     assert n_mismatch(same_stream, want) == 0
     assert n_mismatch(other_stream, want) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+def test_chained_head_calls_see_each_others_results(dtype):
+    """The detection-head kernels are launched as programmatic dependents (a call's CTAs may become resident while
+    the call before it drains) and wait for the complete end of what precedes them before touching memory.  A chain
+    in which every call reads what the previous one wrote -- forward into the features of the next forward, then
+    backward calls accumulating into one gradient tensor -- gives the bits of the same chain run with a device
+    synchronisation after every call."""
+    from medvision_b200 import _C
+    g = torch.Generator().manual_seed(41)
+    N, C, S = 16, 8, 24
+    feat0 = torch.rand(N, C, S, S, generator=g).to(dtype).cuda()
+    b = torch.arange(N).float().view(-1, 1)
+    centre = S / 2 + (torch.rand(N, 2, generator=g) - 0.5) * 4
+    size = S * (0.7 + 0.2 * torch.rand(N, 2, generator=g))
+    ang = (torch.rand(N, 1, generator=g) - 0.5) * 0.6
+    rois = torch.cat([b, centre, size, ang], 1).to(dtype).cuda()       # one roi per sample: output shape == feature shape
+    grad = torch.randn(N, C, S, S, generator=g).to(dtype).cuda()
+
+    def chain(sync):
+        bufs = [feat0, torch.empty_like(feat0), torch.empty_like(feat0)]
+        cur = 0
+        for _ in range(8):
+            nxt = 1 + (cur % 2) if cur else 1
+            _C.roi_align_rotated_2d_forward(bufs[cur], rois, bufs[nxt], S, S, 1.0, 2, True, 1)
+            if sync:
+                torch.cuda.synchronize()
+            cur = nxt
+        result = bufs[cur].clone()
+        gin = torch.zeros_like(feat0, dtype=torch.float32)
+        g32, r32 = grad.float(), rois.float()
+        for _ in range(8):  # every call adds the same contributions to the same addresses
+            _C.roi_align_rotated_2d_backward(g32, r32, gin, S, S, 1.0, 2, True, 1)
+            if sync:
+                torch.cuda.synchronize()
+        return result, gin
+
+    torch.cuda.synchronize()
+    want, gwant = chain(True)
+    for _ in range(5):
+        got, ggot = chain(False)
+        torch.cuda.synchronize()
+        assert n_mismatch(got, want) == 0
+        # eight equal float contributions per address, in whatever order: equal up to the order of float additions
+        assert torch.allclose(ggot, gwant, rtol=1e-5, atol=1e-6)
