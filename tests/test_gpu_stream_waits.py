@@ -126,3 +126,45 @@ def test_chained_head_calls_see_each_others_results(dtype):
         assert n_mismatch(got, want) == 0
         # eight equal float contributions per address, in whatever order: equal up to the order of float additions
         assert torch.allclose(ggot, gwant, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("rot", ["z", "mixed"])
+def test_chained_dense_calls_see_each_others_results(rot):
+    """A dense rotated forward is two overlapped launches, and the head kernel behind it is a programmatic
+    dependent.  A chain of calls in which each resamples the previous result, followed by a head call on the
+    last one, gives the bits of the same chain run with a device synchronisation after every call."""
+    from medvision_b200 import _C
+    g = torch.Generator().manual_seed(43)
+    N, D, H, W = 6, 16, 32, 32
+    feat0 = torch.rand(N, 1, D, H, W, generator=g).half().cuda()
+    ext = torch.tensor([W, H, D], dtype=torch.float32)
+    b = torch.arange(N).float().view(-1, 1)
+    centre = ext / 2 + (torch.rand(N, 3, generator=g) - 0.5) * 2
+    size = ext * (0.8 + 0.3 * torch.rand(N, 3, generator=g))
+    ang = (torch.rand(N, 3, generator=g) - 0.5) * 0.5
+    ang[:, :2] = 0
+    if rot == "mixed":
+        ang[::2, :2] = (torch.rand(N, 2, generator=g)[::2] - 0.5) * 0.5
+    rois = torch.cat([b, centre, size, ang], 1).half().cuda()
+    head_rois = torch.cat([b, centre - size / 4, centre + size / 4], 1).half().cuda()
+
+    def chain(sync):
+        bufs = [feat0, torch.empty_like(feat0), torch.empty_like(feat0)]
+        cur = 0
+        for _ in range(6):
+            nxt = 1 if cur != 1 else 2
+            _C.affine_3d(bufs[cur], rois, bufs[nxt], D, H, W, 1.0, 1, True, 1)
+            if sync:
+                torch.cuda.synchronize()
+            cur = nxt
+        head = torch.empty((N, 1, 3, 3, 3), dtype=torch.float16, device="cuda")
+        _C.roi_align_3d_forward(bufs[cur], head_rois, head, 3, 3, 3, 1.0, 2, 1)
+        return bufs[cur].clone(), head
+
+    torch.cuda.synchronize()
+    want, hwant = chain(True)
+    assert float(want.float().abs().max()) > 0
+    for _ in range(5):
+        got, hgot = chain(False)
+        torch.cuda.synchronize()
+        assert n_mismatch(got, want) == 0 and n_mismatch(hgot, hwant) == 0
