@@ -21,7 +21,6 @@ template <typename T> struct BwdAcc;
 template <> struct BwdAcc<float> { typedef float type; };
 template <> struct BwdAcc<__half> { typedef float type; };
 
-__device__ __forceinline__ void bwd_red(float* p, float v) { atomicAdd(p, v); }  // result unused: a reduction
 // a tap row's two x-neighbours into the float accumulator volume [lo, hi): see atomic_add_pair
 __device__ __forceinline__ void bwd_red_row(float* p0, float* p1, float v0, float v1, const float* lo, const float* hi) {
   atomic_add_pair(p0, p1, v0, v1, lo, hi);
@@ -46,11 +45,10 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
     return;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int kStep = 1;  // a thread's two voxels are neighbours along w
   const int pw0 = k.tw * kS3TileW + (warp & 1) * 16 + (lane & 7) * 2;
   const int ph = k.th * kS3TileH + (warp >> 1) * 4 + (lane >> 3);
   if (ph >= p.oh || pw0 >= p.ow) return;
-  const bool has_b = (pw0 + kStep < p.ow);
+  const bool has_b = (pw0 + 1 < p.ow);
   const long long plane_o = (long long)p.oh * p.ow;
   const T* go = (const T*)p.in + k.nc * p.ovol + (long long)k.pd0 * plane_o + (long long)ph * p.ow + pw0;
   Acc* acc = acc_base + ((long long)g.batch * p.C + k.c) * p.vol;
@@ -60,7 +58,7 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
 
   const T sub_x = lattice_sub<T>(g.bin[0], 0, 1), sub_y = lattice_sub<T>(g.bin[1], 0, 1);
   const T xa = A::add(lattice_base<T>(g.start[0], pw0, g.bin[0], fm), sub_x);
-  const T xb = A::add(lattice_base<T>(g.start[0], has_b ? pw0 + kStep : pw0, g.bin[0], fm), sub_x);
+  const T xb = A::add(lattice_base<T>(g.start[0], has_b ? pw0 + 1 : pw0, g.bin[0], fm), sub_x);
   const T y = A::add(lattice_base<T>(g.start[1], ph, g.bin[1], fm), sub_y);
   const V x2 = Q::make(xa, xb);
 
@@ -113,7 +111,7 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
       const S3ZTap<T> e = sh.zt[i];
       if (!e.inside) continue;
       const T ga = go[i * plane_o];
-      const T gb = has_b ? go[i * plane_o + kStep] : A::fi(0);
+      const T gb = has_b ? go[i * plane_o + 1] : A::fi(0);
       const V g2 = Q::make(ga, gb);
       const V hz2 = Q::dup(e.h), lz2 = Q::dup(e.l);
       const V hzhy = Q::mul(hz2, hy2), hzly = Q::mul(hz2, ly2);
@@ -163,7 +161,7 @@ resample_bwd_stream3d(const Params p, const S3Launch L, typename BwdAcc<T>::type
     const V ry2 = Q::add(Q::add(sxy[1], Q::dup(e.p[1])), c2[1]);
     const V rz2 = Q::add(Q::add(sxy[2], Q::dup(e.p[2])), c2[2]);
     const T rx[2] = {Q::lo(rx2), Q::hi(rx2)}, ry[2] = {Q::lo(ry2), Q::hi(ry2)}, rz[2] = {Q::lo(rz2), Q::hi(rz2)};
-    const T gv[2] = {go[i * plane_o], has_b ? go[i * plane_o + kStep] : A::fi(0)};
+    const T gv[2] = {go[i * plane_o], has_b ? go[i * plane_o + 1] : A::fi(0)};
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       if (s == 1 && !has_b) continue;
