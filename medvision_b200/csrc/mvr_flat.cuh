@@ -57,13 +57,28 @@ __device__ __forceinline__ void flat_grid_dependency() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// type in which the contributions to one cell are summed before they leave (see the backward of resample_flat)
+template <typename T> struct FlatWide;
+template <> struct FlatWide<float> {
+  typedef float type;
+  __device__ __forceinline__ static float narrow(float v) { return v; }
+};
+template <> struct FlatWide<__half> {
+  typedef float type;
+  __device__ __forceinline__ static __half narrow(float v) { return __float2half_rn(v); }
+};
+template <> struct FlatWide<double> {
+  typedef double type;
+  __device__ __forceinline__ static double narrow(double v) { return v; }
+};
+
 // SR: compile-time sampling ratio per axis (1 or 2), or 0 = taken from the roi at run time
 // (any fixed ratio, or the adaptive ceil(bin) grid).
 // OFF: type of the tap offsets inside one channel's volume (int when D*H*W < 2^31).
 template <typename T, int NDIM, int SR, bool BWD, typename OFF>
 // (the 2D half backward is the one instantiation that gains from a full single wave of 16 CTAs per SM: 22.6 against
 // 26.7 us on the rotated 2D head; the float kernels lose more to the 32-register limit than the wave gives)
-__global__ void __launch_bounds__(kFlatThreads, (NDIM == 2 && BWD && sizeof(T) == 2) ? 16 : 1)
+__global__ void __launch_bounds__(kFlatThreads, (NDIM == 2 && BWD && sizeof(T) == 2 && SR != 0) ? 16 : 1)
 resample_flat(const Params p, const FlatDivs fd, int total) {
   typedef Ar<T> A;
   constexpr int fm = kFlatFm;
@@ -115,6 +130,18 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
   const int gx = SR ? SR : g.grid[0], gy = SR ? SR : g.grid[1], gz = (NDIM == 3) ? (SR ? SR : g.grid[2]) : 1;
 
   T acc = zero;
+  // backward with a run-time sample grid: the cell of the volume whose contributions are being summed
+  typedef typename FlatWide<T>::type Wide;
+  OFF cell_off[1 << NDIM];
+  Wide cell_sum[1 << NDIM];
+  bool cell_held = false;
+  auto flush_cell = [&]() {
+    if (!cell_held) return;
+#pragma unroll
+    for (int k = 0; k < (1 << NDIM); k += 2)
+      atomic_add_pair(gvol + cell_off[k], gvol + cell_off[k + 1], FlatWide<T>::narrow(cell_sum[k]),
+                      FlatWide<T>::narrow(cell_sum[k + 1]), glo, ghi);
+  };
   auto sample = [&](T x, T y, T z) {
     T sx, sy, sz;
     to_volume<T, NDIM>(g, p.kind, fm, x, y, z, sx, sy, sz);
@@ -123,11 +150,28 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
     const bool in = make_taps<T, NDIM, OFF>(p.D, p.H, p.W, sz, sy, sx, p.order, w, off);
     if (BWD) {
       if (!in) return;
+      if (SR == 0) {
+        // Run-time sample grids (adaptive, or three and more per axis) put consecutive samples of an output into
+        // the same cell of the volume more often than not (adaptive sampling spaces them at most a voxel apart;
+        // an up-sampling roi puts all of them there): their contributions -- each rounded to the element type as
+        // the reference forms it -- are summed in a wider type per cell and leave once, when the walk leaves the
+        // cell.  Fewer reductions, and the many small addends of an up-sampling roi are no longer lost one by one
+        // against a large half accumulator.
+        if (!cell_held || off[0] != cell_off[0]) {
+          flush_cell();
+#pragma unroll
+          for (int k = 0; k < (1 << NDIM); ++k) { cell_off[k] = off[k]; cell_sum[k] = 0; }
+          cell_held = true;
+        }
+#pragma unroll
+        for (int k = 0; k < (1 << NDIM); ++k) cell_sum[k] += (Wide)A::tof(A::div(A::mul(go, w[k]), g.count_bwd));
+        return;
+      }
 #pragma unroll
       for (int k = 0; k < (1 << NDIM); k += 2) {
         // a fixed ratio makes the sample count a power of two: the division is an exact scaling
-        const T g0 = SR ? A::scale_pow2(A::mul(go, w[k]), inv_count) : A::div(A::mul(go, w[k]), g.count_bwd);
-        const T g1 = SR ? A::scale_pow2(A::mul(go, w[k + 1]), inv_count) : A::div(A::mul(go, w[k + 1]), g.count_bwd);
+        const T g0 = A::scale_pow2(A::mul(go, w[k]), inv_count);
+        const T g1 = A::scale_pow2(A::mul(go, w[k + 1]), inv_count);
         atomic_add_pair(gvol + off[k], gvol + off[k + 1], g0, g1, glo, ghi);
       }
     } else {
@@ -170,6 +214,7 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
       }
     }
   }
+  if (BWD && SR == 0) flush_cell();
   if (!BWD) ((T*)p.out)[e] = SR ? A::scale_pow2(acc, inv_count) : A::div(acc, g.count_fwd);
 }
 
