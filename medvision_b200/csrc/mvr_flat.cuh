@@ -130,7 +130,11 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
   const int gx = SR ? SR : g.grid[0], gy = SR ? SR : g.grid[1], gz = (NDIM == 3) ? (SR ? SR : g.grid[2]) : 1;
 
   T acc = zero;
-  // backward with a run-time sample grid: the cell of the volume whose contributions are being summed
+  // backward: the cell of the volume whose contributions are being summed.  Always for half gradients (the sums are
+  // what keeps the small addends of an up-sampling roi); for float and double only with a run-time sample grid, where
+  // consecutive samples share cells often enough for the saved reductions to pay for the bookkeeping (on the
+  // down-sampling detection heads at ratio 2 it costs 15 % and saves nothing).
+  constexpr bool kCellSums = BWD && (SR == 0 || sizeof(T) == 2);
   typedef typename FlatWide<T>::type Wide;
   OFF cell_off[1 << NDIM];
   Wide cell_sum[1 << NDIM];
@@ -150,13 +154,12 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
     const bool in = make_taps<T, NDIM, OFF>(p.D, p.H, p.W, sz, sy, sx, p.order, w, off);
     if (BWD) {
       if (!in) return;
-      if (SR == 0) {
-        // Run-time sample grids (adaptive, or three and more per axis) put consecutive samples of an output into
-        // the same cell of the volume more often than not (adaptive sampling spaces them at most a voxel apart;
-        // an up-sampling roi puts all of them there): their contributions -- each rounded to the element type as
-        // the reference forms it -- are summed in a wider type per cell and leave once, when the walk leaves the
-        // cell.  Fewer reductions, and the many small addends of an up-sampling roi are no longer lost one by one
-        // against a large half accumulator.
+      if (kCellSums) {
+        // Consecutive samples of an output often fall into the same cell of the volume (adaptive sampling spaces
+        // them at most a voxel apart; an up-sampling roi puts all of them there): their contributions -- each
+        // rounded to the element type as the reference forms it -- are summed in a wider type per cell and leave
+        // once, when the walk leaves the cell.  Fewer reductions, and the many small addends of an up-sampling roi
+        // are no longer lost one by one against a large half accumulator.
         if (!cell_held || off[0] != cell_off[0]) {
           flush_cell();
 #pragma unroll
@@ -164,7 +167,8 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
           cell_held = true;
         }
 #pragma unroll
-        for (int k = 0; k < (1 << NDIM); ++k) cell_sum[k] += (Wide)A::tof(A::div(A::mul(go, w[k]), g.count_bwd));
+        for (int k = 0; k < (1 << NDIM); ++k)
+          cell_sum[k] += (Wide)A::tof(SR ? A::scale_pow2(A::mul(go, w[k]), inv_count) : A::div(A::mul(go, w[k]), g.count_bwd));
         return;
       }
 #pragma unroll
@@ -214,7 +218,7 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
       }
     }
   }
-  if (BWD && SR == 0) flush_cell();
+  if (BWD && kCellSums) flush_cell();
   if (!BWD) ((T*)p.out)[e] = SR ? A::scale_pow2(acc, inv_count) : A::div(acc, g.count_fwd);
 }
 
