@@ -220,17 +220,6 @@ def time_steps(fn, steps, warmup, world):
     return max_over_ranks(e0.elapsed_time(e1), world)
 
 
-def keep_pool_memory():
-    """The half backward borrows its float accumulator volume from the device's stream-ordered memory pool on every
-    call.  By default that pool hands unused memory back to the driver at every synchronisation, and the next call
-    pays for mapping it again; a host that runs the op in a loop raises the pool's release threshold once, as here."""
-    from cuda.bindings import runtime as rt
-    from cuda.bindings.driver import cuuint64_t
-    err, pool = rt.cudaDeviceGetDefaultMemPool(torch.cuda.current_device())
-    if err == rt.cudaError_t.cudaSuccess:
-        rt.cudaMemPoolSetAttribute(pool, rt.cudaMemPoolAttr.cudaMemPoolAttrReleaseThreshold, cuuint64_t(1 << 62))
-
-
 def touched_elements(feat, rois, out_size, order):
     """Exact count of distinct input elements read by the forward (mark pass, untimed)."""
     from medvision_b200 import _lib
@@ -562,8 +551,6 @@ def main():
 
     rank, world, local = dist_setup(args.gpus)
     impl = Ours() if args.impl == "ours" else ReferenceCuda()
-    if args.impl == "ours":
-        keep_pool_memory()
     if args.workload == "det":
         if rank == 0:
             print(json.dumps({"impl": args.impl, "detection": detection_configs(impl)}))

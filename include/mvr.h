@@ -16,8 +16,10 @@
  *      rotated 3D  (R,10) [batch, cx, cy, cz, w, h, d, angle_x, angle_y, angle_z]   (radians)
  *  - Calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
  *    default stream) and never synchronise.  The forward entry points allocate nothing.  The
- *    dense 3D half-precision backward takes a float scratch volume of the gradient's shape from
- *    the device's stream-ordered memory pool (cudaMallocAsync / cudaFreeAsync on `stream`).
+ *    dense 3D half-precision backward takes a float scratch volume of the gradient's shape from a
+ *    stream-ordered memory pool of the library's own (cudaMallocFromPoolAsync / cudaFreeAsync on
+ *    `stream`), which keeps up to 1 GiB of what it was given between calls: see
+ *    mvr_cached_memory_bytes / mvr_release_cached_memory.
  *  - Return value: MVR_OK or a negative MVR_ERR_* code; nothing is launched on error.
  *    `mvr_strerror` gives the message, worded as the reference's AT_ERROR text where one
  *    exists ("wrong roi size! size_rois should be 10", medvision/csrc/roi_align_rotated_3d.h:34-36).
@@ -71,6 +73,12 @@ extern "C" {
 const char* mvr_strerror(int code);
 int mvr_version(void);
 
+/* The memory pool behind the dense 3D half backward (current device).  Bytes the pool holds at
+ * the moment (0 before the first such call), and: give all of it that is not in use back to the
+ * driver.  Neither has a counterpart in the reference, which allocates nothing. */
+long long mvr_cached_memory_bytes(void);
+int mvr_release_cached_memory(void);
+
 /* Which float products are fused into the following addition (bit set of the contraction
  * pattern; half arithmetic never fuses).  The default reproduces the reference build
  * (nvcc -fmad=true).  Returns the previous value.  Process-wide; not a per-call option. */
@@ -117,7 +125,7 @@ int mvr_roi_resample_bwd(const void* grad_out, const void* rois, void* grad_in, 
  *
  * Same arguments, same result and same error codes as mvr_roi_resample_bwd.  The difference is
  * where the float accumulator of the dense 3D half-precision backward lives: the regular entry
- * point borrows it from the stream-ordered memory pool for the duration of the call; this one uses
+ * point borrows it from the library's stream-ordered memory pool for the duration of the call; this one uses
  * a fixed array inside the library image and calls no cudaMalloc / cudaFree / pool routine at all
  * (shapes and element types that need no accumulator volume go to the very same kernels as with
  * the regular entry point, which never allocated for them either).

@@ -41,6 +41,23 @@ def last_status(device=None, clear=True):
     return v
 
 
+def cached_memory_bytes(device=None):
+    """Bytes held by the library's memory pool on ``device`` (the float accumulator volumes of the dense 3D half
+    backward come from it; it keeps up to 1 GiB between calls)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    with torch.cuda.device(index):
+        return int(_lib.lib.mvr_cached_memory_bytes())
+
+
+def release_cached_memory(device=None):
+    """Give the unused part of that pool back to the driver."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    with torch.cuda.device(index):
+        rc = _lib.lib.mvr_release_cached_memory()
+    if rc != 0:
+        raise RuntimeError(_lib.strerror(rc))
+
+
 def _dtype_code(t, what):
     code = _DTYPES.get(t.dtype)
     if code is None:

@@ -52,7 +52,7 @@ PROTOTYPES = {
     "mvr_affine_3d": _ROT3D,
 }
 OTHER_SYMBOLS = ["mvr_strerror", "mvr_version", "mvr_set_float_contraction", "mvr_get_float_contraction",
-                 "mvr_selftest_tma_skip_plane"]
+                 "mvr_selftest_tma_skip_plane", "mvr_cached_memory_bytes", "mvr_release_cached_memory"]
 
 
 def _load():
@@ -72,6 +72,10 @@ def _load():
     lib.mvr_set_float_contraction.argtypes = [_i32]
     lib.mvr_get_float_contraction.restype = _i32
     lib.mvr_selftest_tma_skip_plane.restype = _i32
+    lib.mvr_cached_memory_bytes.restype = ctypes.c_longlong
+    lib.mvr_cached_memory_bytes.argtypes = []
+    lib.mvr_release_cached_memory.restype = _i32
+    lib.mvr_release_cached_memory.argtypes = []
     lib.mvr_selftest_tma_skip_plane.argtypes = [_i32]
     return lib
 

@@ -180,6 +180,27 @@ const char* mvr_strerror(int code) {
 
 int mvr_version(void) { return 1; }
 
+long long mvr_cached_memory_bytes(void) {
+  cudaMemPool_t pool = bwd_pool_of_current_device(false);
+  if (!pool) return 0;
+  unsigned long long bytes = 0;
+  if (cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return (long long)bytes;
+}
+
+int mvr_release_cached_memory(void) {
+  cudaMemPool_t pool = bwd_pool_of_current_device(false);
+  if (!pool) return MVR_OK;
+  if (cudaMemPoolTrimTo(pool, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return MVR_ERR_LAUNCH;
+  }
+  return MVR_OK;
+}
+
 int mvr_selftest_tma_skip_plane(int plane) { return g_t3_selftest_skip_plane.exchange(plane < 0 ? -1 : plane); }
 
 int mvr_set_float_contraction(int bits) { return g_contraction.exchange(bits & 0x00ffffff); }

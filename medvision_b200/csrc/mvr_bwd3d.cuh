@@ -13,6 +13,8 @@
 // voxel.  The result differs from any one run of the reference by less than two runs of the
 // reference differ from each other.
 #pragma once
+#include <mutex>
+
 #include "mvr_stream3d.cuh"
 
 namespace mvr {
@@ -231,9 +233,47 @@ inline int launch_bwd_stream3d_half(const Params& p, const S3Launch& L, long lon
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
+// The memory pool the float accumulator volumes come from: one per device, the library's own.  The device's
+// default pool hands unused memory back to the driver at every synchronisation, so a host that synchronises
+// between steps would pay for mapping the volume again on every call (measured: 0.95 ms became 1.1-1.6 ms); this
+// pool keeps up to kBwdPoolKeepBytes of what it has been given and never touches the settings of the host's pools.
+constexpr unsigned long long kBwdPoolKeepBytes = 1ull << 30;
+constexpr int kBwdPoolMaxDevices = 64;
+struct BwdPools {
+  std::mutex mutex;
+  cudaMemPool_t pool[kBwdPoolMaxDevices] = {};
+};
+inline BwdPools& bwd_pools() {
+  static BwdPools pools;
+  return pools;
+}
+// pool of the current device (created on first use), or nullptr
+inline cudaMemPool_t bwd_pool_of_current_device(bool create) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kBwdPoolMaxDevices) return nullptr;
+  BwdPools& ps = bwd_pools();
+  std::lock_guard<std::mutex> lock(ps.mutex);
+  if (!ps.pool[dev] && create) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t pool = nullptr;
+    if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    unsigned long long keep = kBwdPoolKeepBytes;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    ps.pool[dev] = pool;
+  }
+  return ps.pool[dev];
+}
+
 // Launches the streaming backward when the call has its shape (3D, one sample per voxel, half or
 // float in the reference's contraction pattern); MVR_STREAM3D_NOT_APPLICABLE otherwise.
-// Half needs a float scratch volume: it is taken from the stream-ordered memory pool and
+// Half needs a float scratch volume: it is taken from the library's memory pool on the call's stream and
 // returned to it on the same stream.
 inline int try_launch_bwd_stream3d(const Params& p, int dtype, cudaStream_t st) {
   S3Launch L;
@@ -245,7 +285,8 @@ inline int try_launch_bwd_stream3d(const Params& p, int dtype, cudaStream_t st) 
   }
   const long long n = (long long)p.N * p.C * p.vol;
   float* scratch = nullptr;
-  if (cudaMallocAsync((void**)&scratch, (size_t)n * sizeof(float), st) != cudaSuccess) {
+  cudaMemPool_t pool = bwd_pool_of_current_device(true);
+  if (!pool || cudaMallocFromPoolAsync((void**)&scratch, (size_t)n * sizeof(float), pool, st) != cudaSuccess) {
     cudaGetLastError();
     return MVR_STREAM3D_NOT_APPLICABLE;  // no memory for the scratch volume: element-type atomics instead
   }

@@ -169,14 +169,14 @@ resample_flat(const Params p, const FlatDivs fd, int total) {
 #pragma unroll
         for (int k = 0; k < (1 << NDIM); ++k)
           cell_sum[k] += (Wide)A::tof(SR ? A::scale_pow2(A::mul(go, w[k]), inv_count) : A::div(A::mul(go, w[k]), g.count_bwd));
-        return;
-      }
+      } else {
 #pragma unroll
-      for (int k = 0; k < (1 << NDIM); k += 2) {
-        // a fixed ratio makes the sample count a power of two: the division is an exact scaling
-        const T g0 = A::scale_pow2(A::mul(go, w[k]), inv_count);
-        const T g1 = A::scale_pow2(A::mul(go, w[k + 1]), inv_count);
-        atomic_add_pair(gvol + off[k], gvol + off[k + 1], g0, g1, glo, ghi);
+        for (int k = 0; k < (1 << NDIM); k += 2) {
+          // a fixed ratio makes the sample count a power of two: the division is an exact scaling
+          const T g0 = A::scale_pow2(A::mul(go, w[k]), inv_count);
+          const T g1 = A::scale_pow2(A::mul(go, w[k + 1]), inv_count);
+          atomic_add_pair(gvol + off[k], gvol + off[k + 1], g0, g1, glo, ghi);
+        }
       }
     } else {
       T val = zero;

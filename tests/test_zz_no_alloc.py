@@ -92,8 +92,7 @@ def test_noalloc_backward_refuses_volumes_beyond_its_capacity():
 
 
 def _pool_high_water(reset=False):
-    """High-water mark of the device's default stream-ordered memory pool (the pool the regular entry point
-    borrows its accumulator volume from)."""
+    """High-water mark of the device's default stream-ordered memory pool (which the library must leave alone)."""
     from cuda.bindings import runtime as rt
     dev = torch.cuda.current_device()
     err, pool = rt.cudaDeviceGetDefaultMemPool(dev)
@@ -107,27 +106,32 @@ def _pool_high_water(reset=False):
     return int(used)
 
 
-def test_noalloc_backward_takes_nothing_from_the_memory_pool():
-    """The regular half backward borrows its accumulator from the device's default memory pool; the variant must
-    leave the pool's high-water mark where it was."""
-    from medvision_b200 import _lib
+def test_noalloc_backward_takes_nothing_from_any_memory_pool():
+    """The regular half backward borrows its accumulator from the library's own memory pool; the variant must leave
+    that pool and the device's default pool where they were."""
+    from medvision_b200 import _C, _lib
     L = _lib.lib
     grad, rois, shape = _job(505)
     gin = torch.zeros(shape, dtype=torch.float16, device="cuda")
     assert _call(L.mvr_roi_resample_bwd_noalloc, grad, rois, gin) == 0  # first call: address look-up done
     torch.cuda.synchronize()
-    torch.cuda.current_stream().synchronize()
+    _C.release_cached_memory()
+    assert _C.cached_memory_bytes() == 0
     before = _pool_high_water(reset=True)
     assert _call(L.mvr_roi_resample_bwd_noalloc, grad, rois, gin) == 0
     torch.cuda.synchronize()
-    assert _pool_high_water() == before
-    # ... whereas the regular entry point does borrow from it (the check above can see an allocation)
+    assert _pool_high_water() == before and _C.cached_memory_bytes() == 0
+    # ... whereas the regular entry point does borrow (the check above can see an allocation): from the library's
+    # pool, which keeps the memory for the next call, and not from the device's default pool
     assert _call(L.mvr_roi_resample_bwd, grad, rois, gin) == 0
     torch.cuda.synchronize()
     n = 1
     for s in shape:
         n *= s
-    assert _pool_high_water() >= before + 4 * n
+    assert _C.cached_memory_bytes() >= 4 * n
+    assert _pool_high_water() == before
+    _C.release_cached_memory()
+    assert _C.cached_memory_bytes() == 0
 
 
 @pytest.mark.parametrize("case", ["head3d_ratio2", "plane2d"])
