@@ -19,7 +19,8 @@
  *    dense 3D half-precision backward takes a float scratch volume of the gradient's shape from a
  *    stream-ordered memory pool of the library's own (cudaMallocFromPoolAsync / cudaFreeAsync on
  *    `stream`), which keeps up to 1 GiB of what it was given between calls: see
- *    mvr_cached_memory_bytes / mvr_release_cached_memory.
+ *    mvr_cached_memory_bytes / mvr_release_cached_memory.  The pool is created by the first such
+ *    call on a device; make that call before any stream capture begins.
  *  - Return value: MVR_OK or a negative MVR_ERR_* code; nothing is launched on error.
  *    `mvr_strerror` gives the message, worded as the reference's AT_ERROR text where one
  *    exists ("wrong roi size! size_rois should be 10", medvision/csrc/roi_align_rotated_3d.h:34-36).
